@@ -3,7 +3,8 @@
 //
 // Mechanisms, each with its constants as kernel arguments so other designs can pick them up:
 //   * k_norm_rows       sandwich norm: x += N(y; w_post), optional pass prologue (x += x0, x += step), out = N(x; w_pre),
-//                       N(v; w) = v / sqrt(mean(v^2) + eps) * (1 + w); also the embedding gather (x = scale * E[token]);
+//                       N(v; w) = v / sqrt(mean(v^2) + eps) * (w_off + w); also the embedding gather (x = scale * E[token], optionally
+//                       normalised); with post_plain the sublayer output is added as x += y * w_post (a layer scale behind a pre-norm);
 //   * k_matvec_bf16     decode projection: BF16 weight rows streamed with 128-bit loads, FP32 activation and accumulator,
 //                       bias or gated-activation epilogue (gelu_tanh(g) * u);
 //   * k_gemm_f32 / k_gemm_bf16   prefill projections for any M, N, K: true FP32 on the CUDA cores, or BF16 operands on the
@@ -25,13 +26,14 @@ namespace ly {
 typedef __nv_bfloat16 bf16;
 
 enum { EPI_STORE = 0, EPI_GATED = 1 };   // C = A W^T (+ bias)  |  H = act(A Wg^T) * (A Wu^T) with W = [Wg; Wu] stacked by rows
-enum { ACT_GELU_TANH = 0, ACT_SILU = 1 };
+enum { ACT_GELU_TANH = 0, ACT_SILU = 1, ACT_RELU = 2 };
 
 __device__ __forceinline__ float bf_lo(unsigned v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf_hi(unsigned v) { return __uint_as_float(v & 0xffff0000u); }
 
 __device__ __forceinline__ float act_apply(int act, float z) {
     if (act == ACT_SILU) return z / (1.0f + expf(-z));
+    if (act == ACT_RELU) return fmaxf(z, 0.0f);
     // tanh form of GELU: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
     const float u = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
     return 0.5f * z * (1.0f + tanhf(u));
@@ -86,6 +88,9 @@ struct NormArgs {
     float *trace;        // [n][E]: copy of x after the post-norm part (nullable)
     float eps;
     int E;
+    float w_off;         // added to every norm weight: 1 for weights stored as a deviation from one, 0 for weights used as stored
+    int post_plain;      // 1: x += y * w_post (no statistic of y: a layer scale)
+    const float *w_emb;  // [E] (nullable): the gathered embedding row is normalised, x = N(scale * emb[token]; w_emb)
 };
 #define LY_NORM_THREADS 256
 
@@ -102,15 +107,29 @@ __global__ void __launch_bounds__(LY_NORM_THREADS) k_norm_rows(NormArgs a) {
             row[i] = v;
             if (a.x0) a.x0[src + i] = v;
         }
+        if (a.w_emb) {
+            __syncthreads();
+            float ss = 0.0f;
+            for (int i = tid; i < E; i += LY_NORM_THREADS) ss = fmaf(row[i], row[i], ss);
+            ss = block_sum(ss, red);
+            const float inv = 1.0f / sqrtf(ss / (float)E + a.eps);
+            for (int i = tid; i < E; i += LY_NORM_THREADS) {
+                const float v = row[i] * inv * (a.w_off + a.w_emb[i]);
+                row[i] = v;
+                if (a.x0) a.x0[src + i] = v;
+            }
+        }
     } else {
         for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] = a.x[src + i];
     }
-    if (a.y) {
+    if (a.y && a.post_plain) {
+        for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] = fmaf(a.y[src + i], a.w_post[i], row[i]);
+    } else if (a.y) {
         float ss = 0.0f;
         for (int i = tid; i < E; i += LY_NORM_THREADS) { const float v = a.y[src + i]; ss = fmaf(v, v, ss); }
         ss = block_sum(ss, red);
         const float inv = 1.0f / sqrtf(ss / (float)E + a.eps);
-        for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] += a.y[src + i] * inv * (1.0f + a.w_post[i]);
+        for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] += a.y[src + i] * inv * (a.w_off + a.w_post[i]);
     }
     if (a.trace)
         for (int i = tid; i < E; i += LY_NORM_THREADS) a.trace[src + i] = row[i];
@@ -126,7 +145,7 @@ __global__ void __launch_bounds__(LY_NORM_THREADS) k_norm_rows(NormArgs a) {
         ss = block_sum(ss, red);
         const float inv = 1.0f / sqrtf(ss / (float)E + a.eps);
         for (int i = tid; i < E; i += LY_NORM_THREADS) {
-            const float v = row[i] * inv * (1.0f + a.w_pre[i]);
+            const float v = row[i] * inv * (a.w_off + a.w_pre[i]);
             if (a.out32) a.out32[dst + i] = v;
             if (a.out16) a.out16[dst + i] = __float2bfloat16_rn(v);
         }
@@ -441,6 +460,13 @@ struct WindowAttn {
     int gate;                    // 1: the output is multiplied by sigmoid(g), g the fourth block of the fused projection
     int gate_off;                // column of g in a projection row; < 0: behind q | k | v (heads*dk + kv_heads*dk + kv_heads*dv)
     float eps;
+    int k_heads;                 // key heads when they differ from the value heads (0: kv_heads): query head h reads key head h / (heads / k_heads).
+                                 // Scores mixed over the heads are folded into the query (k_rope_mix_prep): every head then reads ONE key row
+                                 // made of all key heads (k_heads = 1, dk = key heads * key size) while the values keep their own heads
+    const float *sink_logit;     // [heads] (nullable: 0): with sink, the denominator carries exp(sink_logit[h]) instead of exp(0)
+    const float *gate_src;       // the gate is read from row r of this buffer (row stride gate_ld) instead of the query's row (nullable)
+    int gate_ld;
+    int gate_heads;              // 1: ONE gate per head (g has `heads` entries) instead of one per output entry
 };
 // Row layout of the fused projection output: [q: heads*dk | k: kv_heads*dk | v: kv_heads*dv | g: heads*dv]
 
@@ -507,6 +533,8 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
     const int splits = gridDim.z, z = blockIdx.z;
     const int qd = a.heads * a.dk, kd = a.kv_heads * a.dk, vd = a.kv_heads * a.dv;
     const int g = h / (a.heads / a.kv_heads);
+    const int gk = a.k_heads > 0 ? h / (a.heads / a.k_heads) : g;
+    const float sink_v = a.sink_logit ? a.sink_logit[h] : 0.0f;
     const int pos = st->pos + r;
     int lo = pos - a.window + 1 > 0 ? pos - a.window + 1 : 0;
     int nk = pos - lo + 1;
@@ -520,7 +548,7 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
     const float *q = P + (size_t)r * ldp + (size_t)h * a.dk;
     for (int i = tid; i < a.dk; i += LY_ATT_THREADS) qs[i] = q[i];
     __syncthreads();
-    float mx = (a.sink && splits == 1) ? 0.0f : -INFINITY; // the sink's logit takes part in the maximum (split runs: when the parts are merged)
+    float mx = (a.sink && splits == 1) ? sink_v : -INFINITY; // the sink's logit takes part in the maximum (split runs: when the parts are merged)
     {
         const bool vec = (a.dk & 3) == 0 && (a.ldk & 3) == 0;
         int lpk = 32; // lanes per key
@@ -543,7 +571,7 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
                 for (int u = 0; u < 4; u++) {
                     const int j = j0 + u * stride + ks;
                     kv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (has && j < nk) kv[u] = *reinterpret_cast<const float4 *>(kc + (size_t)((lo + j) % a.ring) * a.ldk + (size_t)g * a.dk + 4 * sub);
+                    if (has && j < nk) kv[u] = *reinterpret_cast<const float4 *>(kc + (size_t)((lo + j) % a.ring) * a.ldk + (size_t)gk * a.dk + 4 * sub);
                 }
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
@@ -558,7 +586,7 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
                 const int j = j0 + ks;
                 float d = 0.0f;
                 if (j < nk) {
-                    const float *kr = kc + (size_t)((lo + j) % a.ring) * a.ldk + (size_t)g * a.dk;
+                    const float *kr = kc + (size_t)((lo + j) % a.ring) * a.ldk + (size_t)gk * a.dk;
                     if (vec) {
                         for (int c = sub; c < a.dk / 4; c += lpk) {
                             const float4 kv = *reinterpret_cast<const float4 *>(kr + 4 * c), qv = *reinterpret_cast<const float4 *>(qs + 4 * c);
@@ -581,10 +609,12 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
         sum += w;
     }
     sum = block_sum(sum, red); // also orders the sc[] writes before the reads below
-    const float inv = splits > 1 ? 1.0f : 1.0f / (sum + (a.sink ? expf(-mx) : 0.0f)); // split runs keep the unnormalised sum
+    const float inv = splits > 1 ? 1.0f : 1.0f / (sum + (a.sink ? expf(sink_v - mx) : 0.0f)); // split runs keep the unnormalised sum
     const size_t cell = (size_t)r * a.heads + h; // (row, head)
     float *my_o = splits > 1 ? ks_.o + (cell * splits + z) * a.dv : nullptr;
-    const float *gate = P + (size_t)r * ldp + (a.gate_off >= 0 ? a.gate_off : qd + kd + vd) + (size_t)h * a.dv;
+    const float *gate = (a.gate_src ? a.gate_src + (size_t)r * a.gate_ld : P + (size_t)r * ldp) + (a.gate_off >= 0 ? a.gate_off : qd + kd + vd) +
+                        (a.gate_heads ? (size_t)h : (size_t)h * a.dv);
+    const int gs = a.gate_heads ? 0 : 1; // stride of the gate over the output entries of a head
     const int vw = ((a.dv & 3) == 0 && (a.ldv & 3) == 0) ? 4 : 1; // value elements per thread
     int tpk = (a.dv + vw - 1) / vw;                             // threads per key
     if (tpk > LY_ATT_THREADS) tpk = LY_ATT_THREADS;
@@ -613,7 +643,7 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
                 for (int k = 0; k < groups; k++) o += part[e * LY_ATT_THREADS + k * tpk + dl];
                 if (splits > 1) { my_o[d + e] = o; continue; }
                 o *= inv;
-                if (a.gate) o *= 1.0f / (1.0f + expf(-gate[d + e]));
+                if (a.gate) o *= 1.0f / (1.0f + expf(-gate[(d + e) * gs]));
                 store_out<OUT_T>(out + (size_t)r * ldo + (size_t)h * a.dv + d + e, o);
             }
         }
@@ -627,9 +657,9 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    float M = a.sink ? 0.0f : -INFINITY;
+    float M = a.sink ? sink_v : -INFINITY;
     for (int k = 0; k < splits; k++) M = fmaxf(M, __ldcg(ks_.ml + (cell * splits + k) * 2));
-    float Lsum = a.sink ? expf(-M) : 0.0f;
+    float Lsum = a.sink ? expf(sink_v - M) : 0.0f;
     for (int k = 0; k < splits; k++) {
         const float mk = __ldcg(ks_.ml + (cell * splits + k) * 2);
         if (mk != -INFINITY) Lsum += __ldcg(ks_.ml + (cell * splits + k) * 2 + 1) * expf(mk - M);
@@ -641,7 +671,7 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
             if (mk != -INFINITY) o += __ldcg(ks_.o + (cell * splits + k) * a.dv + d) * expf(mk - M);
         }
         o /= Lsum;
-        if (a.gate) o *= 1.0f / (1.0f + expf(-gate[d]));
+        if (a.gate) o *= 1.0f / (1.0f + expf(-gate[d * gs]));
         store_out<OUT_T>(out + (size_t)r * ldo + (size_t)h * a.dv + d, o);
     }
     if (tid == 0) ks_.count[cell] = 0u; // ready for the next launch
@@ -689,8 +719,10 @@ __global__ void __launch_bounds__(LY_ATT_MMA_THREADS) k_window_attention_mma(con
     float *sbias = reinterpret_cast<float *>(smraw + QT + 2 * KT + 2 * VT);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int h = blockIdx.y, r0 = blockIdx.x * BM;
-    const int kd = a.kv_heads * DK, vd = a.kv_heads * DV, qd = a.heads * DK;
+    const int kd = a.ldk, vd = a.ldv, qd = a.heads * DK; // row strides of the BF16 twin rings = those of the FP32 rings
     const int kvh = h / (a.heads / a.kv_heads);
+    const int kh = a.k_heads > 0 ? h / (a.heads / a.k_heads) : kvh;
+    const float sink_v = a.sink_logit ? a.sink_logit[h] : 0.0f;
     const int pos0 = st->pos;
     const int rows = n - r0 < BM ? n - r0 : BM;
     const int q_lo = pos0 + r0, q_hi = pos0 + r0 + rows - 1;
@@ -704,7 +736,7 @@ __global__ void __launch_bounds__(LY_ATT_MMA_THREADS) k_window_attention_mma(con
             const bool ok = kt0 + r <= q_hi;
             int sl = slot0 + r;
             if (sl >= a.ring) sl = a.ring >= 64 ? sl - a.ring : sl % a.ring;
-            cp_async16(&Kd[r][c], kc16 + (ok ? (size_t)sl * kd + (size_t)kvh * DK + c : 0), ok);
+            cp_async16(&Kd[r][c], kc16 + (ok ? (size_t)sl * kd + (size_t)kh * DK + c : 0), ok);
         }
         for (int e = tid; e < 64 * (DV / 8); e += LY_ATT_MMA_THREADS) {
             const int r = e / (DV / 8), c = (e % (DV / 8)) * 8;
@@ -746,7 +778,7 @@ __global__ void __launch_bounds__(LY_ATT_MMA_THREADS) k_window_attention_mma(con
 #pragma unroll
         for (int e = 0; e < 4; e++) o[j][e] = 0.0f;
     float mrow[2], lrow[2];
-    mrow[0] = mrow[1] = a.sink ? 0.0f : -INFINITY;
+    mrow[0] = mrow[1] = a.sink ? sink_v : -INFINITY; // the sink: a running softmax that starts at (maximum z, denominator exp(z - z))
     lrow[0] = lrow[1] = a.sink ? 1.0f : 0.0f;
     const int prow[2] = {pos0 + r0 + warp * 16 + g, pos0 + r0 + warp * 16 + g + 8}; // positions of this thread's two rows
     const bool vrow[2] = {warp * 16 + g < rows, warp * 16 + g + 8 < rows};
@@ -845,12 +877,14 @@ __global__ void __launch_bounds__(LY_ATT_MMA_THREADS) k_window_attention_mma(con
         if (!vrow[rr]) continue;
         const int r = r0 + warp * 16 + g + rr * 8;
         const float inv = lrow[rr] > 0.0f ? 1.0f / lrow[rr] : 0.0f;
-        const float *gate = P + (size_t)r * ldp + (a.gate_off >= 0 ? a.gate_off : qd + kd + vd) + (size_t)h * DV;
+        const float *gate = (a.gate_src ? a.gate_src + (size_t)r * a.gate_ld : P + (size_t)r * ldp) + (a.gate_off >= 0 ? a.gate_off : qd + kd + vd) +
+                            (a.gate_heads ? (size_t)h : (size_t)h * DV);
+        const float ghead = a.gate && a.gate_heads ? 1.0f / (1.0f + expf(-gate[0])) : 1.0f;
 #pragma unroll
         for (int j = 0; j < DV / 8; j++) {
             const int d = j * 8 + 2 * t;
-            float v0 = o[j][2 * rr] * inv, v1 = o[j][2 * rr + 1] * inv;
-            if (a.gate) {
+            float v0 = o[j][2 * rr] * inv * ghead, v1 = o[j][2 * rr + 1] * inv * ghead;
+            if (a.gate && !a.gate_heads) {
                 const float2 gv = *reinterpret_cast<const float2 *>(gate + d);
                 v0 *= 1.0f / (1.0f + expf(-gv.x));
                 v1 *= 1.0f / (1.0f + expf(-gv.y));

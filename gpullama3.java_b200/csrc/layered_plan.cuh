@@ -15,11 +15,17 @@
 // q|k|v|gate projection (+bias) -> whole-projection q/k norm + ring write -> window attention (+gate) -> output projection ->
 // norm -> gated feed-forward projection (activation in the epilogue) -> down projection.
 //
-// Two block kinds share the plan: the sandwich block above (B200_BLOCK_SANDWICH) and the parallel block of latent_plan.cuh
-// (B200_BLOCK_PARALLEL: latent attention and a mixture of experts reading two norms of the same residual row).
+// Three block kinds share the plan: the sandwich block above (B200_BLOCK_SANDWICH), the pre-norm block (B200_BLOCK_PRENORM: the
+// same sequence with x += s * y in place of the post-norm, RMS norms that carry one number, a normalised embedding, and loop
+// passes without a prologue) and the parallel block of latent_plan.cuh (B200_BLOCK_PARALLEL: latent attention and a mixture of
+// experts reading two norms of the same residual row).  Sandwich and pre-norm layers choose their mixer per layer: windowed
+// attention (optionally with rotation, values taken from the keys, head temperatures and head-mixed scores: k_rope_mix_prep
+// replaces k_qk_prep) or the gated delta rule (k_delta_prep -> k_delta_rule -> k_head_norm_gate), whose recurrent state and
+// convolution inputs live per RUN next to the rings.
 #pragma once
 #include "layered.cuh"
 #include "latent.cuh"
+#include "delta.cuh"
 
 struct LyLayer {
     b200_layer_spec s{};
@@ -48,6 +54,16 @@ struct LyLayer {
     CUtensorMap m_moe_gate, m_moe_up, m_moe_down, m_moe_h; // mixture of experts on the tcgen05 GEMM: all experts' matrices in one map each
     bool tc_moe = false;
     bool tc_proj = false, tc_o = false, tc_gu = false, tc_down = false;
+    // windowed attention with rotation / head temperature / head mixing (k_rope_mix_prep): pv = value rows and gr = gate rows of the
+    // fused projection; the query the attention kernels read has heads * dk_eff entries (dk_eff = kv_heads * key_dim when the head
+    // mixing is folded into it, k_heads = key heads the attention kernel indexes)
+    int pv = 0, gr = 0, dk_eff = 0, k_heads = 0;
+    bool mixprep = false;
+    float *temp = nullptr, *talk = nullptr, *sink_logit = nullptr;
+    float *ls1 = nullptr, *ls2 = nullptr; // pre-norm block: layer scales
+    // gated delta rule: convolution weights of the q | k | v channels, per-head constants, weight of the read-out norm
+    float *conv_w = nullptr, *a_log = nullptr, *dt_bias = nullptr, *onorm = nullptr;
+    int dC = 0; // convolved channels = 2 * kv_heads * key_dim + heads * value_dim
 };
 struct LyRun {
     int layer = 0, pass = -1;
@@ -58,6 +74,7 @@ struct LyRun {
     bool tc_lat = false;
     int kw = 0, vw = 0;                        // floats per cache row (latent attention: one cache, kw = kv_rank + rot_dim, vc == nullptr)
     bool own = true;                           // false: kc is the cache of the run this layer reads (kv_from)
+    float *S = nullptr, *cstate = nullptr;     // gated delta rule: state [heads][key_dim][value_dim]; ring of convolution inputs [cring][channels]
 };
 struct Layered {
     b200_layered_config c{};
@@ -96,6 +113,12 @@ struct Layered {
     int *moe_ids = nullptr, *moe_perm = nullptr, *tile_group = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr;
     int maxQ = 0, maxL = 0, maxQU = 0, maxTop = 0, maxExperts = 0, max_tiles = 0, max_att_dv = 1;
     std::vector<std::pair<std::vector<float>, float *>> rope_tables; // (key, device table)
+    // pre-norm block / gated delta rule
+    float w_off = 1.0f;   // what the norm kernels add to a norm weight (sandwich: weights are deviations from one)
+    bool prenorm = false;
+    float *emb_norm = nullptr;
+    float *DLT = nullptr, *DO = nullptr; // prepared q | k | v | beta | decay rows and read-out rows of a delta layer, [cap][...]
+    int maxD = 0, maxDO = 0, cring = 0, max_taps = 0;
 };
 
 // What ly_project needs to take the tcgen05 route: operand and result descriptors (nullptr = CUDA-core / mma.sync kernels).
@@ -116,6 +139,22 @@ static int ly_vec_f32(b200_plan *p, const b200_tensor *tensors, int nt, const st
         for (int64_t i = 0; i < n; i++) { uint32_t u = (uint32_t)s[i] << 16; memcpy(&h[i], &u, 4); }
     } else if (t->ggml_type == B200_GGML_F32) memcpy(h.data(), t->data, (size_t)n * 4);
     else return fail(p, B200_ERR_UNSUPPORTED, "tensor %s: type %d (vectors are BF16 or F32)", name.c_str(), t->ggml_type);
+    int rc;
+    if ((rc = dalloc(p, dst, (size_t)n * 4))) return rc;
+    CK(cudaMemcpy(*dst, h.data(), (size_t)n * 4, cudaMemcpyHostToDevice));
+    return B200_OK;
+}
+
+// A tensor that holds ONE number (BF16 or F32, any rank), repeated n times: a norm whose weight is the same for all coordinates.
+static int ly_scalar_vec(b200_plan *p, const b200_tensor *tensors, int nt, const std::string &name, int64_t n, float **dst) {
+    const b200_tensor *t = find(tensors, nt, name);
+    if (!t) return fail(p, B200_ERR_BAD_ARG, "missing tensor %s", name.c_str());
+    if (n_elems(t) != 1) return fail(p, B200_ERR_BAD_ARG, "tensor %s has %lld elements, expected one number", name.c_str(), (long long)n_elems(t));
+    float v;
+    if (t->ggml_type == B200_GGML_BF16) { uint32_t u = (uint32_t)(*(const uint16_t *)t->data) << 16; memcpy(&v, &u, 4); }
+    else if (t->ggml_type == B200_GGML_F32) memcpy(&v, t->data, 4);
+    else return fail(p, B200_ERR_UNSUPPORTED, "tensor %s: type %d (numbers are BF16 or F32)", name.c_str(), t->ggml_type);
+    std::vector<float> h((size_t)n, v);
     int rc;
     if ((rc = dalloc(p, dst, (size_t)n * 4))) return rc;
     CK(cudaMemcpy(*dst, h.data(), (size_t)n * 4, cudaMemcpyHostToDevice));
@@ -152,14 +191,17 @@ static void ly_free(b200_plan *p) {
 static size_t ly_att_smem(int dk, int window) { return ly::att_smem_floats(dk, window) * 4; }
 static size_t ly_att_smem(const b200_layer_spec &s, int ring) {
     (void)ring;
-    // latent attention attends over the cached row [latent | shared key part] with one key/value head
-    return ly_att_smem(s.mixer == B200_MIXER_LATENT_ATTENTION ? s.kv_rank + s.rot_dim : s.key_dim, s.window);
+    // latent attention attends over the cached row [latent | shared key part] with one key/value head; head-mixed scores over a row of all key heads
+    return ly_att_smem(s.mixer == B200_MIXER_LATENT_ATTENTION ? s.kv_rank + s.rot_dim : s.head_mix ? s.kv_heads * s.key_dim : s.key_dim, s.window);
 }
 
 // Instances of the tensor-core prefill attention: (key size, value size) = (64, 64), (128, 128), (192, 128); 0 = none.
-static int ly_mma_kind(int dk, int dv) { return dk == 64 && dv == 64 ? 1 : dk == 128 && dv == 128 ? 2 : dk == 192 && dv == 128 ? 3 : 0; }
+static int ly_mma_kind(int dk, int dv) {
+    return dk == 64 && dv == 64 ? 1 : dk == 128 && dv == 128 ? 2 : dk == 192 && dv == 128 ? 3 : dk == 128 && dv == 64 ? 4 : dk == 256 && dv == 128 ? 5 : 0;
+}
 static size_t ly_mma_smem(int kind, int window) {
-    return kind == 1 ? ly::att_mma_smem_bytes<64, 64>(window) : kind == 2 ? ly::att_mma_smem_bytes<128, 128>(window) : ly::att_mma_smem_bytes<192, 128>(window);
+    return kind == 1 ? ly::att_mma_smem_bytes<64, 64>(window) : kind == 2 ? ly::att_mma_smem_bytes<128, 128>(window) : kind == 3 ? ly::att_mma_smem_bytes<192, 128>(window)
+         : kind == 4 ? ly::att_mma_smem_bytes<128, 64>(window) : ly::att_mma_smem_bytes<256, 128>(window);
 }
 static int ly_launch_mma(b200_plan *p, int kind, int n, int heads, int window, const float *P, int ldp, const ly::WindowAttn &wa, const ly::bf16 *k16, const ly::bf16 *v16,
                          const StepState *st, ly::bf16 *out, int ldo) {
@@ -167,6 +209,8 @@ static int ly_launch_mma(b200_plan *p, int kind, int n, int heads, int window, c
     const size_t sm = ly_mma_smem(kind, window);
     if (kind == 1) return launch_k(p, false, ly::k_window_attention_mma<64, 64>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
     if (kind == 2) return launch_k(p, false, ly::k_window_attention_mma<128, 128>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
+    if (kind == 4) return launch_k(p, false, ly::k_window_attention_mma<128, 64>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
+    if (kind == 5) return launch_k(p, false, ly::k_window_attention_mma<256, 128>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
     return launch_k(p, false, ly::k_window_attention_mma<192, 128>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
 }
 
@@ -177,7 +221,12 @@ static ly::WindowAttn ly_attn_args(const Layered &Y, const LyLayer &L) {
     a.ldk = L.kd; a.ldv = L.vd;
     a.scale = L.s.score_scale; a.softcap = L.s.softcap;
     a.rel = L.rel; a.bucket = L.bucket; a.qnorm = L.qnorm; a.knorm = L.knorm;
-    a.sink = L.s.sink; a.gate = L.s.gate; a.gate_off = -1; a.eps = Y.c.norm_eps;
+    a.sink = L.s.sink; a.gate = L.s.gate; a.gate_off = L.qd + L.kd + L.pv; a.eps = Y.c.norm_eps;
+    a.sink_logit = L.sink_logit; a.gate_heads = L.s.gate == 2;
+    if (L.mixprep) { // the query comes from k_rope_mix_prep's buffer (temperature and head mixing folded in), the gate from the projection row
+        a.dk = L.dk_eff; a.k_heads = L.k_heads; a.qnorm = a.knorm = nullptr;
+        a.gate_src = Y.PROJ; a.gate_ld = Y.maxP;
+    }
     return a;
 }
 
@@ -198,7 +247,7 @@ static int ly_project(b200_plan *p, bool decode, int n, const float *a32, const 
         int rc;
         if (EPI == ly::EPI_GATED)
             rc = pg::gemm2_persist_launch<pg::GEMM_GATEUP, 256, pg::GEMM2_PERSIST_STAGES_256>(*tc->a, *tc->b, *tc->b2, *tc->c, c16, ldc, n, mt2, N / 128, K, p->n_sms, p->stream, 1,
-                                                                                            pg::FLAVOR_BF16 | pg::FLAVOR_GELU_BF16);
+                                                                                            pg::FLAVOR_BF16 | (act == B200_ACT_RELU ? pg::FLAVOR_RELU_BF16 : act == B200_ACT_SILU ? pg::FLAVOR_SILU_BF16 : pg::FLAVOR_GELU_BF16));
         else if (N % 256 == 0) {
             // a narrow output (N = width) leaves most SMs idle: split K over the grid and let every split reduce-add its partial
             // product into the zeroed result through TMA, as the GGUF prefill does for its residual GEMMs
@@ -236,8 +285,9 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
     float *pend_trace = nullptr;
     auto norm = [&](bool embed, bool add_x0, const float *step, const float *w_pre) {
         ly::NormArgs a{};
-        a.x = Y.X; a.x0 = Y.has_loop ? Y.X0 : nullptr;
+        a.x = Y.X; a.x0 = Y.has_loop && !Y.prenorm ? Y.X0 : nullptr;
         a.y = pend_y; a.w_post = pend_w;
+        a.w_off = Y.w_off; a.post_plain = Y.prenorm ? 1 : 0; a.w_emb = embed ? Y.emb_norm : nullptr;
         a.emb = embed ? Y.emb : nullptr; a.tokens = tokens; a.st = st; a.emb_scale = Y.c.embedding_scale;
         a.add_x0 = add_x0 ? 1 : 0; a.step = step; a.w_pre = w_pre;
         a.out32 = w_pre && !h16 ? Y.A32 : nullptr; a.out16 = w_pre && h16 ? Y.A16 : nullptr;
@@ -249,7 +299,9 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
     for (size_t r = 0; r < Y.runs.size(); r++) {
         const LyRun &R = Y.runs[r];
         const LyLayer &L = Y.layers[R.layer];
-        if ((rc = norm(r == 0, R.first && R.pass > 0, R.first ? Y.step + (size_t)R.pass * E : nullptr, L.norm1))) return rc;
+        // a loop pass of a sandwich block starts with x += x0 (not the first pass) and x += step[pass]; a pre-norm block just repeats
+        const bool prologue = R.first && !Y.prenorm;
+        if ((rc = norm(r == 0, prologue && R.pass > 0, prologue ? Y.step + (size_t)R.pass * E : nullptr, L.norm1))) return rc;
         LyTc t_proj, t_o, t_gu, t_down;
         if (Y.tc && !decode) {
             if (L.tc_proj) { t_proj.a = &Y.m_a; t_proj.b = &L.m_proj; t_proj.c = &Y.m_proj_c; }
@@ -258,29 +310,51 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
             if (L.tc_down) { t_down.a = &L.m_h; t_down.b = &L.m_down; t_down.c = &Y.m_y_c; }
         }
         // the q, k, v biases are added where the projection is consumed (k_qk_prep), so every projection kernel serves it
-        if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.A32, Y.A16, L.w_proj, nullptr, L.P, E, Y.PROJ, nullptr, Y.maxP, 0, &t_proj))) return rc;
+        if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.A32, Y.A16, L.w_proj, nullptr, decode ? L.Pn : L.P, E, Y.PROJ, nullptr, Y.maxP, 0, &t_proj))) return rc;
         nl++;
+        if (L.s.mixer == B200_MIXER_GATED_DELTA) {
+            ly::DeltaArgs da{};
+            da.heads = L.s.heads; da.kv_heads = L.s.kv_heads; da.dk = L.s.key_dim; da.dv = L.s.value_dim; da.taps = L.s.conv_taps; da.cring = Y.cring;
+            da.conv_w = L.conv_w; da.a_log = L.a_log; da.dt_bias = L.dt_bias; da.unit_eps = 1e-6f;
+            if ((rc = launch_k(p, false, ly::k_delta_prep, dim3(n), dim3(256), (size_t)L.dC * 4, (const float *)Y.PROJ, Y.maxP, da, R.cstate, Y.DLT, Y.maxD, st))) return rc;
+            if ((rc = launch_k(p, false, ly::k_delta_rule, dim3(L.s.heads, (L.s.value_dim + DELTA_COLS - 1) / DELTA_COLS), dim3(DELTA_COLS), ly::delta_rule_smem_floats(L.s.key_dim) * 4,
+                               (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st))) return rc;
+            if ((rc = launch_k(p, false, ly::k_head_norm_gate, dim3(n), dim3(256), (size_t)0, (const float *)Y.DO, Y.maxDO, (const float *)(Y.PROJ + L.dC + 2 * L.s.heads), Y.maxP,
+                               (const float *)L.onorm, L.s.heads, L.s.value_dim, Y.c.norm_eps, h16 ? (float *)nullptr : Y.ATT32, h16 ? Y.ATT16 : (ly::bf16 *)nullptr, L.gd))) return rc;
+            nl += 3;
+        } else {
         const ly::WindowAttn wa = ly_attn_args(Y, L);
-        if ((rc = launch_k(p, false, ly::k_qk_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, wa, (const float *)L.b_proj, R.kc, R.vc, R.kc16, R.vc16, st))) return rc;
+        const float *qsrc = Y.PROJ; // where the attention kernels read the query rows
+        int ldq = Y.maxP;
+        if (L.mixprep) {
+            ly::RopeMixArgs ra{};
+            ra.heads = L.s.heads; ra.kv_heads = L.s.kv_heads; ra.dk = L.s.key_dim; ra.dv = L.s.value_dim; ra.rope_dims = L.s.rope_dims; ra.rope_layout = L.s.rope_layout;
+            ra.cs = L.rope; ra.temp = L.temp; ra.talk = L.talk; ra.value_from_key = L.s.value_from_key; ra.ring = Y.ring;
+            qsrc = Y.Q; ldq = L.s.heads * L.dk_eff;
+            rc = launch_k(p, false, ly::k_rope_mix_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, ra, (const float *)L.b_proj, Y.Q, ldq, R.kc, R.vc, R.kc16, R.vc16, st);
+        } else
+            rc = launch_k(p, false, ly::k_qk_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, wa, (const float *)L.b_proj, R.kc, R.vc, R.kc16, R.vc16, st);
+        if (rc) return rc;
         nl++;
         const size_t asm_ = ly_att_smem(L.s, Y.ring);
-        const int mma = ly_mma_kind(L.s.key_dim, L.s.value_dim);
+        const int mma = ly_mma_kind(L.mixprep ? L.dk_eff : L.s.key_dim, L.s.value_dim);
         if (h16 && R.kc16 && mma)
-            rc = ly_launch_mma(p, mma, n, L.s.heads, L.s.window, (const float *)Y.PROJ, Y.maxP, wa, (const ly::bf16 *)R.kc16, (const ly::bf16 *)R.vc16, st, Y.ATT16, L.gd);
-        else if (h16) rc = launch_k(p, false, ly::k_window_attention<ly::bf16>, dim3(n, L.s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
+            rc = ly_launch_mma(p, mma, n, L.s.heads, L.s.window, qsrc, ldq, wa, (const ly::bf16 *)R.kc16, (const ly::bf16 *)R.vc16, st, Y.ATT16, L.gd);
+        else if (h16) rc = launch_k(p, false, ly::k_window_attention<ly::bf16>, dim3(n, L.s.heads), dim3(LY_ATT_THREADS), asm_, qsrc, ldq, wa,
                                (const float *)R.kc, (const float *)R.vc, st, Y.ATT16, L.gd, ly::KeySplit{nullptr, nullptr, nullptr});
         else {
             // the decode step has one row and few heads: split every head's window over several CTAs so that the SMs are used
             int sp = 1;
             if (decode && Y.split.o && L.s.window >= 64) { sp = p->n_sms / L.s.heads; if (sp > Y.max_splits) sp = Y.max_splits; if (sp < 1) sp = 1; }
-            rc = launch_k(p, false, ly::k_window_attention<float>, dim3(n, L.s.heads, sp), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
+            rc = launch_k(p, false, ly::k_window_attention<float>, dim3(n, L.s.heads, sp), dim3(LY_ATT_THREADS), asm_, qsrc, ldq, wa,
                           (const float *)R.kc, (const float *)R.vc, st, Y.ATT32, L.gd, sp > 1 ? Y.split : ly::KeySplit{nullptr, nullptr, nullptr});
         }
         if (rc) return rc;
         nl++;
+        } // windowed attention
         if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.ATT32, Y.ATT16, L.w_o, nullptr, E, L.gd, Y.Y, nullptr, E, 0, &t_o))) return rc;
         nl++;
-        pend_y = Y.Y; pend_w = L.norm1b;
+        pend_y = Y.Y; pend_w = Y.prenorm ? L.ls1 : L.norm1b;
         if (L.s.ff_kind == B200_FF_DENSE_GATED) {
             if ((rc = norm(false, false, nullptr, L.norm2))) return rc;
             const int F = L.s.ff_dim;
@@ -288,7 +362,7 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
             nl++;
             if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.H32, Y.H16, L.w_down, nullptr, E, F, Y.Y, nullptr, E, 0, &t_down))) return rc;
             nl++;
-            pend_y = Y.Y; pend_w = L.norm2b;
+            pend_y = Y.Y; pend_w = Y.prenorm ? L.ls2 : L.norm2b;
         }
         pend_trace = trace ? trace + r * (size_t)Y.cap * E : nullptr;
     }
@@ -338,7 +412,7 @@ static int ly_tc_init(b200_plan *p) {
         L.tc_proj = fits(L.P, E) && Y.maxP % 4 == 0 && pg::make_map(&L.m_proj, L.w_proj, L.P, E, 128) == 0;
         L.tc_o = fits(E, L.gd) && pg::make_map(&L.m_o, L.w_o, E, L.gd, 128) == 0 && pg::make_map(&L.m_att, Y.ATT16, rows, L.gd, pg::BM) == 0;
         if (L.w_gu && L.s.ff_kind == B200_FF_DENSE_GATED) {
-            L.tc_gu = fits(F, E) && L.s.ff_act == B200_ACT_GELU_TANH && pg::make_map(&L.m_gate, L.w_gu, F, E, 128) == 0 &&
+            L.tc_gu = fits(F, E) && pg::make_map(&L.m_gate, L.w_gu, F, E, 128) == 0 &&
                       pg::make_map(&L.m_up, L.w_gu + (size_t)F * E, F, E, 128) == 0;
             L.tc_down = fits(E, F) && pg::make_map(&L.m_down, L.w_down, E, F, 128) == 0 && pg::make_map(&L.m_h, Y.H16, rows, F, pg::BM) == 0;
         }
@@ -375,8 +449,10 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     Layered &Y = *Yp;
     Y.c = *cfg;
     const b200_layered_config &c = Y.c;
-    if (c.arch != B200_ARCH_PIBIDRA && c.arch != B200_ARCH_LATUSUN) return fail(p, B200_ERR_UNSUPPORTED, "unknown layered arch %d", c.arch);
-    if (c.block != B200_BLOCK_SANDWICH && c.block != B200_BLOCK_PARALLEL) return fail(p, B200_ERR_BAD_ARG, "unknown block kind %d", c.block);
+    if (c.arch != B200_ARCH_PIBIDRA && c.arch != B200_ARCH_LATUSUN && c.arch != B200_ARCH_LEROSUN) return fail(p, B200_ERR_UNSUPPORTED, "unknown layered arch %d", c.arch);
+    if (c.block != B200_BLOCK_SANDWICH && c.block != B200_BLOCK_PARALLEL && c.block != B200_BLOCK_PRENORM) return fail(p, B200_ERR_BAD_ARG, "unknown block kind %d", c.block);
+    Y.prenorm = c.block == B200_BLOCK_PRENORM;
+    Y.w_off = Y.prenorm ? 0.0f : 1.0f;
     const bool par = c.block == B200_BLOCK_PARALLEL;
     if (par && Y.has_loop && c.loop_stop > c.loop_start) return fail(p, B200_ERR_UNSUPPORTED, "parallel blocks do not loop");
     if (c.width <= 0 || c.vocab_size <= 0 || c.n_layers <= 0 || c.context_length <= 0) return fail(p, B200_ERR_BAD_ARG, "width, vocabulary, layers and context must be positive");
@@ -431,19 +507,50 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             if (L.s.window > Y.max_window) Y.max_window = L.s.window;
             continue;
         }
-        if (s.mixer != B200_MIXER_WINDOW_ATTENTION) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: mixer %d", l, s.mixer);
+        if (s.mixer != B200_MIXER_WINDOW_ATTENTION && s.mixer != B200_MIXER_GATED_DELTA) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: mixer %d", l, s.mixer);
+        if (s.mixer == B200_MIXER_GATED_DELTA) L.s.window = 1; // a recurrent state, no ring
         if (s.heads <= 0 || s.kv_heads <= 0 || s.heads % s.kv_heads || s.key_dim <= 0 || s.value_dim <= 0 || s.window <= 0)
             return fail(p, B200_ERR_BAD_ARG, "layer %d: heads %d / kv heads %d / key %d / value %d / window %d", l, s.heads, s.kv_heads, s.key_dim, s.value_dim, s.window);
+        if (s.ff_kind != B200_FF_NONE && s.ff_kind != B200_FF_DENSE_GATED) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: feed-forward kind %d", l, s.ff_kind);
+        if (s.ff_kind == B200_FF_DENSE_GATED && (s.ff_dim <= 0 || (s.ff_act != B200_ACT_GELU_TANH && s.ff_act != B200_ACT_SILU && s.ff_act != B200_ACT_RELU)))
+            return fail(p, B200_ERR_BAD_ARG, "layer %d: feed-forward width %d / activation %d", l, s.ff_dim, s.ff_act);
+        if (s.ff_kind == B200_FF_DENSE_GATED && s.ff_dim > Y.maxF) Y.maxF = s.ff_dim;
+        const bool pad = !Y.f32 && E % 64 == 0; // zero rows up to whole 128-row tiles: the BF16 prefill takes the tcgen05 GEMM; the decode step streams Pn rows
+        if (s.mixer == B200_MIXER_GATED_DELTA) {
+            if (s.conv_taps < 1 || s.conv_taps > 64) return fail(p, B200_ERR_BAD_ARG, "layer %d: %d convolution taps", l, s.conv_taps);
+            L.qd = L.kd = s.kv_heads * s.key_dim; L.vd = L.pv = L.gd = L.gr = s.heads * s.value_dim;
+            L.dC = 2 * L.qd + L.vd;
+            L.Pn = L.dC + 2 * s.heads + L.gr;
+            L.P = pad ? (L.Pn + 127) / 128 * 128 : L.Pn;
+            if (ly::delta_rule_smem_floats(s.key_dim) * 4 > (size_t)Y.smem_max || (size_t)L.dC * 4 > (size_t)Y.smem_max)
+                return fail(p, B200_ERR_UNSUPPORTED, "layer %d: a state tile of key size %d or %d convolved channels exceed the shared memory of a CTA", l, s.key_dim, L.dC);
+            if (L.P > Y.maxP) Y.maxP = L.P;
+            if (L.gd > Y.maxO) Y.maxO = L.gd;
+            if (L.dC + 2 * s.heads > Y.maxD) Y.maxD = L.dC + 2 * s.heads;
+            if (L.gd > Y.maxDO) Y.maxDO = L.gd;
+            if (s.conv_taps > Y.max_taps) Y.max_taps = s.conv_taps;
+            continue;
+        }
+        if (s.sink < 0 || s.sink > 2 || s.gate < 0 || s.gate > 2) return fail(p, B200_ERR_BAD_ARG, "layer %d: sink %d / gate %d", l, s.sink, s.gate);
+        if (s.rope_dims < 0 || s.rope_dims % 2 || s.rope_dims > s.key_dim || (s.rope_dims > 0 && !(s.rope_base > 0.0f)) || s.yarn_factor != 0.0f)
+            return fail(p, B200_ERR_BAD_ARG, "layer %d: rotation of %d of %d entries, base %g", l, s.rope_dims, s.key_dim, (double)s.rope_base);
+        if (s.value_from_key && s.value_dim != s.key_dim) return fail(p, B200_ERR_BAD_ARG, "layer %d: values taken from the keys need value size %d = key size %d", l, s.value_dim, s.key_dim);
+        L.mixprep = s.rope_dims > 0 || s.value_from_key || s.head_temp || s.head_mix;
+        if (L.mixprep && s.qk_norm) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: whole-projection q/k norm together with rotation, key-values, head temperature or head mixing", l);
         if (s.bias_rows < 0 || (s.bias_rows > 0 && (s.bias_rows < 2 || !(s.bias_far > s.bias_rows / 2))))
             return fail(p, B200_ERR_BAD_ARG, "layer %d: distance table of %d rows up to %g", l, s.bias_rows, (double)s.bias_far);
-        if (s.ff_kind != B200_FF_NONE && s.ff_kind != B200_FF_DENSE_GATED) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: feed-forward kind %d", l, s.ff_kind);
-        if (s.ff_kind == B200_FF_DENSE_GATED && (s.ff_dim <= 0 || (s.ff_act != B200_ACT_GELU_TANH && s.ff_act != B200_ACT_SILU)))
-            return fail(p, B200_ERR_BAD_ARG, "layer %d: feed-forward width %d / activation %d", l, s.ff_dim, s.ff_act);
         L.qd = s.heads * s.key_dim; L.kd = s.kv_heads * s.key_dim; L.vd = s.kv_heads * s.value_dim; L.gd = s.heads * s.value_dim;
-        L.P = L.Pn = L.qd + L.kd + L.vd + (s.gate ? L.gd : 0);
+        L.pv = s.value_from_key ? 0 : L.vd;
+        L.gr = s.gate == 2 ? s.heads : s.gate ? L.gd : 0;
+        L.P = L.Pn = L.qd + L.kd + L.pv + L.gr;
+        if (L.mixprep) {
+            if (pad) L.P = (L.Pn + 127) / 128 * 128;
+            L.dk_eff = s.head_mix ? L.kd : s.key_dim;
+            L.k_heads = s.head_mix ? 1 : s.kv_heads;
+            if (s.heads * L.dk_eff > Y.maxQ) Y.maxQ = s.heads * L.dk_eff;
+        }
         if (L.P > Y.maxP) Y.maxP = L.P;
         if (L.gd > Y.maxO) Y.maxO = L.gd;
-        if (s.ff_kind == B200_FF_DENSE_GATED && s.ff_dim > Y.maxF) Y.maxF = s.ff_dim;
         if (s.window > Y.max_window) Y.max_window = s.window;
         if (s.value_dim > Y.max_att_dv) Y.max_att_dv = s.value_dim;
     }
@@ -467,6 +574,10 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             CK(set_max_dyn(ly::k_window_attention_mma<64, 64>, Y.smem_max));
             CK(set_max_dyn(ly::k_window_attention_mma<128, 128>, Y.smem_max));
             CK(set_max_dyn(ly::k_window_attention_mma<192, 128>, Y.smem_max));
+            CK(set_max_dyn(ly::k_window_attention_mma<128, 64>, Y.smem_max));
+            CK(set_max_dyn(ly::k_window_attention_mma<256, 128>, Y.smem_max));
+            CK(set_max_dyn(ly::k_delta_prep, Y.smem_max));
+            CK(set_max_dyn(ly::k_delta_rule, Y.smem_max));
             attrs = true;
         }
     }
@@ -507,9 +618,12 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     if ((rc = ly_mat(p, tensors, nt, "embed", c.vocab_size, E, Y.emb, 0))) return rc;
     if ((rc = dalloc(p, &Y.head, (size_t)c.vocab_size * E * 2))) return rc;
     if ((rc = ly_mat(p, tensors, nt, "head", c.vocab_size, E, Y.head, 0))) return rc;
-    if ((rc = ly_vec_f32(p, tensors, nt, "final.norm", E, &Y.final_norm))) return rc;
+    if (Y.prenorm) {
+        if ((rc = ly_scalar_vec(p, tensors, nt, "final.norm", E, &Y.final_norm))) return rc;
+        if ((rc = ly_scalar_vec(p, tensors, nt, "embed.norm", E, &Y.emb_norm))) return rc;
+    } else if ((rc = ly_vec_f32(p, tensors, nt, "final.norm", E, &Y.final_norm))) return rc;
     if (par && (rc = ly_vec_f32(p, tensors, nt, "final.norm.b", E, &Y.final_norm_b))) return rc;
-    if (Y.has_loop && c.loop_times > 0)
+    if (Y.has_loop && c.loop_times > 0 && !Y.prenorm)
         if ((rc = ly_vec_f32(p, tensors, nt, "loop.step", (int64_t)c.loop_times * E, &Y.step))) return rc;
     for (int l = 0; l < c.n_layers; l++) {
         LyLayer &L = Y.layers[l];
@@ -519,19 +633,51 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             if ((rc = ly_latent_upload(p, l, L, tensors, nt))) return rc;
             continue;
         }
-        if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm1", E, &L.norm1))) return rc;
-        if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm1b", E, &L.norm1b))) return rc;
+        if (Y.prenorm) {
+            if ((rc = ly_scalar_vec(p, tensors, nt, pre + "norm1", E, &L.norm1))) return rc;
+            if ((rc = ly_vec_f32(p, tensors, nt, pre + "ls1", E, &L.ls1))) return rc;
+        } else {
+            if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm1", E, &L.norm1))) return rc;
+            if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm1b", E, &L.norm1b))) return rc;
+        }
         if ((rc = dalloc(p, &L.w_proj, (size_t)L.P * E * 2))) return rc;
+        if (L.P > L.Pn) CK(cudaMemset(L.w_proj + (size_t)L.Pn * E, 0, (size_t)(L.P - L.Pn) * E * 2));
         if ((rc = ly_mat(p, tensors, nt, mx + "q", L.qd, E, L.w_proj, 0))) return rc;
         if ((rc = ly_mat(p, tensors, nt, mx + "k", L.kd, E, L.w_proj, L.qd))) return rc;
-        if ((rc = ly_mat(p, tensors, nt, mx + "v", L.vd, E, L.w_proj, L.qd + L.kd))) return rc;
-        if (s.gate && (rc = ly_mat(p, tensors, nt, mx + "g", L.gd, E, L.w_proj, L.qd + L.kd + L.vd))) return rc;
+        if (L.pv > 0 && (rc = ly_mat(p, tensors, nt, mx + "v", L.pv, E, L.w_proj, L.qd + L.kd))) return rc;
+        if (s.mixer == B200_MIXER_GATED_DELTA) {
+            // fused projection rows: q | k | v | b | a | g; the convolution weights of the q | k | v channels in one table
+            if ((rc = ly_mat(p, tensors, nt, mx + "b", s.heads, E, L.w_proj, L.dC))) return rc;
+            if ((rc = ly_mat(p, tensors, nt, mx + "a", s.heads, E, L.w_proj, L.dC + s.heads))) return rc;
+            if ((rc = ly_mat(p, tensors, nt, mx + "g", L.gr, E, L.w_proj, L.dC + 2 * s.heads))) return rc;
+            std::vector<float> cw((size_t)L.dC * s.conv_taps);
+            const char *nm[3] = {"q.conv", "k.conv", "v.conv"};
+            const int off[3] = {0, L.qd, 2 * L.qd}, len[3] = {L.qd, L.kd, L.vd};
+            for (int k = 0; k < 3; k++) {
+                const b200_tensor *t = find(tensors, nt, mx + nm[k]);
+                if (!t || t->ggml_type != B200_GGML_BF16 || t->n_dims != 2 || t->dims[0] != s.conv_taps || t->dims[1] != len[k])
+                    return fail(p, B200_ERR_BAD_ARG, "tensor %s%s: BF16 [%d][%d] expected", mx.c_str(), nm[k], len[k], s.conv_taps);
+                const uint16_t *src = (const uint16_t *)t->data;
+                for (int64_t i = 0; i < (int64_t)len[k] * s.conv_taps; i++) { uint32_t u = (uint32_t)src[i] << 16; memcpy(&cw[(size_t)off[k] * s.conv_taps + i], &u, 4); }
+            }
+            if ((rc = dalloc(p, &L.conv_w, cw.size() * 4))) return rc;
+            CK(cudaMemcpy(L.conv_w, cw.data(), cw.size() * 4, cudaMemcpyHostToDevice));
+            if ((rc = ly_vec_f32(p, tensors, nt, mx + "A_log", s.heads, &L.a_log))) return rc;
+            if ((rc = ly_vec_f32(p, tensors, nt, mx + "dt_bias", s.heads, &L.dt_bias))) return rc;
+            if ((rc = ly_vec_f32(p, tensors, nt, mx + "norm", s.value_dim, &L.onorm))) return rc;
+        } else {
+        if (s.gate && (rc = ly_mat(p, tensors, nt, mx + "g", L.gr, E, L.w_proj, L.qd + L.kd + L.pv))) return rc;
+        if (s.head_temp && (rc = ly_vec_f32(p, tensors, nt, mx + "temp", s.heads, &L.temp))) return rc;
+        if (s.head_mix && (rc = ly_vec_f32(p, tensors, nt, mx + "talk", (int64_t)s.heads * s.heads, &L.talk))) return rc;
+        if (s.sink == 2 && (rc = ly_vec_f32(p, tensors, nt, mx + "sink", s.heads, &L.sink_logit))) return rc;
+        if (s.rope_dims > 0 && (rc = ly_rope_table(p, s, c.context_length, &L.rope))) return rc;
         { // biases of q, k, v in one vector; the gate has none
             std::vector<float> b((size_t)L.P, 0.0f);
             const char *nm[3] = {"q.b", "k.b", "v.b"};
-            const int off[3] = {0, L.qd, L.qd + L.kd}, len[3] = {L.qd, L.kd, L.vd};
+            const int off[3] = {0, L.qd, L.qd + L.kd}, len[3] = {L.qd, L.kd, L.pv};
             bool any = false;
             for (int k = 0; k < 3; k++) {
+                if (len[k] == 0) continue;
                 const b200_tensor *t = find(tensors, nt, mx + nm[k]);
                 if (!t) { if (s.qkv_bias) return fail(p, B200_ERR_BAD_ARG, "missing tensor %s%s", mx.c_str(), nm[k]); continue; }
                 if (n_elems(t) != len[k] || t->ggml_type != B200_GGML_BF16) return fail(p, B200_ERR_BAD_ARG, "tensor %s%s: %d BF16 values expected", mx.c_str(), nm[k], len[k]);
@@ -555,12 +701,18 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             if ((rc = dalloc(p, &L.bucket, (size_t)s.window * 4))) return rc;
             CK(cudaMemcpy(L.bucket, bk.data(), (size_t)s.window * 4, cudaMemcpyHostToDevice));
         }
+        } // windowed attention
         if ((rc = dalloc(p, &L.w_o, (size_t)E * L.gd * 2))) return rc;
         if ((rc = ly_mat(p, tensors, nt, mx + "o", E, L.gd, L.w_o, 0))) return rc;
         if (s.ff_kind == B200_FF_DENSE_GATED) {
             const int F = s.ff_dim;
-            if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm2", E, &L.norm2))) return rc;
-            if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm2b", E, &L.norm2b))) return rc;
+            if (Y.prenorm) {
+                if ((rc = ly_scalar_vec(p, tensors, nt, pre + "norm2", E, &L.norm2))) return rc;
+                if ((rc = ly_vec_f32(p, tensors, nt, pre + "ls2", E, &L.ls2))) return rc;
+            } else {
+                if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm2", E, &L.norm2))) return rc;
+                if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm2b", E, &L.norm2b))) return rc;
+            }
             if ((rc = dalloc(p, &L.w_gu, (size_t)2 * F * E * 2))) return rc;
             if ((rc = ly_mat(p, tensors, nt, ff + "gate", F, E, L.w_gu, 0))) return rc;
             if ((rc = ly_mat(p, tensors, nt, ff + "up", F, E, L.w_gu, F))) return rc;
@@ -572,6 +724,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     p->up.total_s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t_up0).count();
 
     // per-run rings
+    Y.cring = Y.max_taps > 0 ? Y.max_taps - 1 + Y.cap : 0;
     for (LyRun &R : Y.runs) {
         const LyLayer &L = Y.layers[R.layer];
         if (L.s.mixer == B200_MIXER_LATENT_ATTENTION) {
@@ -586,13 +739,22 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             }
             continue;
         }
+        if (L.s.mixer == B200_MIXER_GATED_DELTA) {
+            // the run's recurrent state and its ring of convolution inputs (position j in slot j % cring)
+            const size_t sb = (size_t)L.s.heads * L.s.key_dim * L.s.value_dim * 4, cb = (size_t)Y.cring * L.dC * 4;
+            if ((rc = dalloc(p, &R.S, sb))) return rc;
+            if ((rc = dalloc(p, &R.cstate, cb))) return rc;
+            CK(cudaMemset(R.S, 0, sb));
+            CK(cudaMemset(R.cstate, 0, cb));
+            continue;
+        }
         R.kw = L.kd; R.vw = L.vd;
         if ((rc = dalloc(p, &R.kc, (size_t)Y.ring * L.kd * 4))) return rc;
         if ((rc = dalloc(p, &R.vc, (size_t)Y.ring * L.vd * 4))) return rc;
         CK(cudaMemset(R.kc, 0, (size_t)Y.ring * L.kd * 4));
         CK(cudaMemset(R.vc, 0, (size_t)Y.ring * L.vd * 4));
         // tensor-core prefill attention: BF16 plans, key = value size 64 or 128, a window whose tiles fit shared memory
-        const int kind = ly_mma_kind(L.s.key_dim, L.s.value_dim);
+        const int kind = ly_mma_kind(L.mixprep ? L.dk_eff : L.s.key_dim, L.s.value_dim);
         if (!Y.f32 && Y.att_mma && Y.cap > 1 && kind && ly_mma_smem(kind, L.s.window) <= (size_t)Y.smem_max && Y.maxP % 4 == 0) {
             if ((rc = dalloc(p, &R.kc16, (size_t)Y.ring * L.kd * 2))) return rc;
             if ((rc = dalloc(p, &R.vc16, (size_t)Y.ring * L.vd * 2))) return rc;
@@ -607,7 +769,9 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     const int maxF = Y.maxF > 0 ? Y.maxF : 1;
     const size_t slots = Y.maxTop > 0 ? (size_t)Y.maxTop : 1; // feed-forward rows per token (a mixture of experts: one per chosen expert)
     if ((rc = dalloc(p, &Y.X, cap * E * 4))) return rc;
-    if (Y.has_loop && (rc = dalloc(p, &Y.X0, cap * E * 4))) return rc;
+    if (Y.has_loop && !Y.prenorm && (rc = dalloc(p, &Y.X0, cap * E * 4))) return rc;
+    if (!par && Y.maxQ > 0 && (rc = dalloc(p, &Y.Q, cap * Y.maxQ * 4))) return rc;
+    if (Y.maxD > 0 && ((rc = dalloc(p, &Y.DLT, cap * Y.maxD * 4)) || (rc = dalloc(p, &Y.DO, cap * Y.maxDO * 4)))) return rc;
     if ((rc = dalloc(p, &Y.Y, cap * E * 4))) return rc;
     if ((rc = dalloc(p, &Y.PROJ, cap * Y.maxP * 4))) return rc;
     if ((rc = dalloc(p, &Y.A32, rows32 * E * 4))) return rc;
@@ -735,7 +899,7 @@ static int ly_batch(b200_plan *p, const int32_t *tokens, int n, int start_pos, c
             if ((rc = launch_k(p, false, ly::k_block_norm_rows, dim3(m), dim3(LY_NORM_THREADS), (size_t)E * 4, a))) return rc;
         } else {
             ly::NormArgs a{};
-            a.x = Y.X; a.w_pre = Y.final_norm; a.gather = Y.rows; a.eps = Y.c.norm_eps; a.E = E;
+            a.x = Y.X; a.w_pre = Y.final_norm; a.gather = Y.rows; a.eps = Y.c.norm_eps; a.E = E; a.w_off = Y.w_off;
             a.out32 = Y.f32 ? Y.A32 : nullptr; a.out16 = Y.f32 ? nullptr : Y.A16;
             if ((rc = launch_k(p, false, ly::k_norm_rows, dim3(m), dim3(LY_NORM_THREADS), (size_t)E * 4, a))) return rc;
         }
@@ -756,7 +920,12 @@ static int ly_batch(b200_plan *p, const int32_t *tokens, int n, int start_pos, c
 static int ly_kv_reset(b200_plan *p) {
     Layered &Y = *p->ly;
     for (LyRun &R : Y.runs) {
-        if (!R.own) continue;
+        if (R.S) {
+            const LyLayer &L = Y.layers[R.layer];
+            CK(cudaMemsetAsync(R.S, 0, (size_t)L.s.heads * L.s.key_dim * L.s.value_dim * 4, p->stream));
+            CK(cudaMemsetAsync(R.cstate, 0, (size_t)Y.cring * L.dC * 4, p->stream));
+        }
+        if (!R.own || !R.kc) continue;
         CK(cudaMemsetAsync(R.kc, 0, (size_t)Y.ring * R.kw * 4, p->stream));
         if (R.vc) CK(cudaMemsetAsync(R.vc, 0, (size_t)Y.ring * R.vw * 4, p->stream));
     }
@@ -778,6 +947,11 @@ static int ly_read_buffer(b200_plan *p, const char *name, int layer, void *dst, 
         src = s == "key_cache" ? Y.runs[layer].kc : Y.runs[layer].vc;
         sz = (size_t)Y.ring * (s == "key_cache" ? Y.runs[layer].kw : Y.runs[layer].vw) * 4;
         if (!src) return fail(p, B200_ERR_BAD_ARG, "run %d has no %s", layer, name);
+    } else if (s == "delta_state" || s == "conv_state") {
+        if (layer < 0 || layer >= (int)Y.runs.size() || !Y.runs[layer].S) return fail(p, B200_ERR_BAD_ARG, "run %d has no %s", layer, name);
+        const LyLayer &L = Y.layers[Y.runs[layer].layer];
+        src = s == "delta_state" ? Y.runs[layer].S : Y.runs[layer].cstate;
+        sz = s == "delta_state" ? (size_t)L.s.heads * L.s.key_dim * L.s.value_dim * 4 : (size_t)Y.cring * L.dC * 4;
     } else return fail(p, B200_ERR_BAD_ARG, "unknown buffer %s", name);
     if (bytes < sz) sz = bytes;
     CK(cudaSetDevice(p->device));

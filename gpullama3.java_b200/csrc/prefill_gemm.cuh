@@ -58,7 +58,8 @@ constexpr uint32_t UMMA_IDESC_AB_BF16 = (1u << 7) | (1u << 10);
 //   FLAVOR_BF16       operands are BF16 instead of FP16 (same bytes per element, same TMA maps);
 //   FLAVOR_GELU_BF16  the gate/up epilogue emits bf16(gelu_tanh(g) * u) instead of f16(silu(g) * u).
 //   FLAVOR_SILU_BF16  the gate/up epilogue emits bf16(silu(g) * u).
-enum { FLAVOR_BF16 = 1u, FLAVOR_GELU_BF16 = 2u, FLAVOR_SILU_BF16 = 4u };
+//   FLAVOR_RELU_BF16  the gate/up epilogue emits bf16(max(g, 0) * u).
+enum { FLAVOR_BF16 = 1u, FLAVOR_GELU_BF16 = 2u, FLAVOR_SILU_BF16 = 4u, FLAVOR_RELU_BF16 = 8u };
 // Grouped rows (a mixture of experts; single-CTA kernel): the rows of A are sorted by group and every group is padded to whole
 // 128-row tiles, so an M tile belongs to ONE group: tile_group[m tile] (-1: no work) selects the weight matrix, whose rows start
 // b_rows * group further down the B tensor map(s).  row_scale (nullable) multiplies gate and up before the activation (a weight
@@ -69,6 +70,10 @@ struct Grouped {
     const float *row_scale;
 };
 __device__ __forceinline__ uint32_t gated_pair(uint32_t flavor, float g0, float g1, float u0, float u1) {
+    if (flavor & FLAVOR_RELU_BF16) {
+        const __nv_bfloat162 hh = __floats2bfloat162_rn(fmaxf(g0, 0.0f) * u0, fmaxf(g1, 0.0f) * u1);
+        return *reinterpret_cast<const uint32_t *>(&hh);
+    }
     if (flavor & FLAVOR_SILU_BF16) {
         const __nv_bfloat162 hh = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
         return *reinterpret_cast<const uint32_t *>(&hh);

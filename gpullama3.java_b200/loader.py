@@ -23,6 +23,7 @@ ARCH_QWEN3 = 1
 ARCH_PHI3 = 2
 ARCH_PIBIDRA = 3
 ARCH_LATUSUN = 4
+ARCH_LEROSUN = 5
 
 GGML_BF16 = 30  # ggml's id for bfloat16; layered plans take their safetensors tensors under it
 _SAFETENSORS_TYPES = {"BF16": GGML_BF16, "F16": GGMLType.F16, "F32": GGMLType.F32}
@@ -83,6 +84,14 @@ class LayerSpec:
     rope_layout: str = "half"   # "half": pair (i, i + dims/2) | "interleaved": pair (2i, 2i + 1)
     rope_base: float = 10000.0
     yarn: tuple = (0.0, 0.0, 0.0, 0.0)  # (factor, original length, fast, slow); factor 0: plain frequencies
+    # windowed attention, each switchable on its own (rope_dims > 0 additionally rotates the leading entries of every query / key head)
+    sink_learned: bool = False  # the sink's logit is a learned number per head instead of zero
+    gate_per_head: bool = False  # one sigmoid gate per head instead of one per output entry
+    value_from_key: bool = False  # no value projection: the values are the unrotated keys
+    head_temp: bool = False     # a learned factor per head on the scores
+    head_mix: bool = False      # scores mixed over the query heads before the softmax
+    # gated delta rule: heads = value heads, kv_heads = query / key heads
+    conv_taps: int = 0
 
 
 @dataclass
@@ -97,7 +106,9 @@ class LayeredConfiguration:
     layers: list = field(default_factory=list)
     loop: tuple | None = None  # (start, stop, times): layers [start, stop) run `times` passes over the same weights
     quantization: str = "BF16"
-    block: str = "sandwich"    # "sandwich": x += N(mixer(N x)); x += N(ff(N x)) | "parallel": x += mult * (mixer(LN1 x) + ff(LN2 x))
+    # "sandwich": x += N(mixer(N x)); x += N(ff(N x)) | "parallel": x += mult * (mixer(LN1 x) + ff(LN2 x)) |
+    # "prenorm": x += s1 * mixer(R x); x += s2 * ff(R x), R an RMS norm with one number as weight
+    block: str = "sandwich"
     residual_mult: float = 1.0
     logit_softcap: float = 0.0
 
@@ -225,8 +236,38 @@ def latusun_configuration(cfg: dict, tensor_shapes: dict, context_length: int) -
         block="parallel", residual_mult=float(cfg.get("residual_mult", 1.0)), logit_softcap=float(cfg.get("logit_softcap") or 0.0))
 
 
+def lerosun_configuration(cfg: dict, tensor_shapes: dict, context_length: int) -> LayeredConfiguration:
+    """config.json of a Lerosun model -> LayeredConfiguration: pre-norm blocks whose mixer is a sliding-window attention (partial
+    rotation, values = unrotated keys, per-head temperature, head-mixed scores, learned sink, per-head gate) or a gated delta rule,
+    and a gated ReLU feed-forward.  Every size and every constant that can differ between models comes from the file."""
+    layers = []
+    for i, lc in enumerate(cfg["layers"]):
+        m, mlp = lc["mixer"], lc.get("mlp")
+        if mlp is not None and mlp.get("kind") != "dense":
+            raise UnsupportedModel(f"layer {i}: feed-forward kind {mlp.get('kind')!r}")
+        ff = dict(ff_dim=int(mlp["ff"]) if mlp is not None else 0, ff_act="relu")
+        if lc["type"] == "attention":
+            rot = m.get("rot")
+            layers.append(LayerSpec(
+                heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), key_dim=int(m["dim"]), value_dim=int(m["vdim"]), window=int(m["mask"]["size"]),
+                bias_rows=0, bias_far=0.0, score_scale=float(m["scale"]), softcap=0.0, sink=True, gate=True, qkv_bias=True, qk_norm=False,
+                rope_dims=int(rot["dims"]) if rot else 0, rope_layout="half", rope_base=float(rot["base"]) if rot else 10000.0,
+                sink_learned=True, gate_per_head=True, value_from_key=True, head_temp=True, head_mix=True, **ff))
+        elif lc["type"] == "delta":
+            layers.append(LayerSpec(
+                heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), key_dim=int(m["dim"]), value_dim=int(m["vdim"]), window=1, bias_rows=0, bias_far=0.0,
+                score_scale=1.0, softcap=0.0, sink=False, gate=True, qkv_bias=False, qk_norm=False, mixer="gated_delta", conv_taps=int(m["conv"]), **ff))
+        else:
+            raise UnsupportedModel(f"layer {i}: mixer type {lc['type']!r} (Lerosun layers are 'attention' or 'delta')")
+    loop = cfg.get("loop")
+    return LayeredConfiguration(
+        ARCH_LEROSUN, int(cfg["width"]), int(cfg["vocab"]), int(context_length), float(cfg["norm"]["eps"]), 1.0, layers,
+        (int(loop["start"]), int(loop["stop"]), int(loop["times"])) if loop else None, block="prenorm")
+
+
 # config.json "architecture" -> (model type, configuration builder): the registry of safetensors model directories
-CONFIG_ARCHITECTURES = {"Pibidra": ("PIBIDRA", pibidra_configuration), "Latusun": ("LATUSUN", latusun_configuration)}
+CONFIG_ARCHITECTURES = {"Pibidra": ("PIBIDRA", pibidra_configuration), "Latusun": ("LATUSUN", latusun_configuration),
+                        "Lerosun": ("LEROSUN", lerosun_configuration)}
 DEFAULT_LAYERED_CONTEXT = 4096
 
 

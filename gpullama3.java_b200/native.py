@@ -40,7 +40,7 @@ class LayerSpec(C.Structure):
                [(n, C.c_int32) for n in ("sink", "gate", "qkv_bias", "qk_norm", "ff_kind", "ff_dim", "ff_act")] + \
                [(n, C.c_int32) for n in ("rot_dim", "kv_rank", "kv_from", "rope_dims", "rope_layout")] + \
                [(n, C.c_float) for n in ("rope_base", "yarn_factor", "yarn_original", "yarn_fast", "yarn_slow")] + \
-               [(n, C.c_int32) for n in ("ff_experts", "ff_top")]
+               [(n, C.c_int32) for n in ("ff_experts", "ff_top", "value_from_key", "head_temp", "head_mix", "conv_taps")]
 
 
 class LayeredConfig(C.Structure):
@@ -51,11 +51,11 @@ class LayeredConfig(C.Structure):
 
 
 COMPUTE_BF16, COMPUTE_F32 = 0, 1
-ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
-MIXERS = {"window_attention": 1, "latent_attention": 2}
+ACTIVATIONS = {"gelu_tanh": 0, "silu": 1, "relu": 2}
+MIXERS = {"window_attention": 1, "latent_attention": 2, "gated_delta": 3}
 FF_KINDS = {"none": 0, "dense": 1, "moe": 2}
 ROPE_LAYOUTS = {"half": 0, "interleaved": 1}
-BLOCKS = {"sandwich": 0, "parallel": 1}
+BLOCKS = {"sandwich": 0, "parallel": 1, "prenorm": 2}
 
 
 class Tensor(C.Structure):

@@ -74,7 +74,10 @@ def make_layered_config(model: Model, compute: str = "bfloat16"):
         sp.mixer = native.MIXERS[s.mixer]
         sp.heads, sp.kv_heads, sp.key_dim, sp.value_dim, sp.window = s.heads, s.kv_heads, s.key_dim, s.value_dim, s.window
         sp.bias_rows, sp.bias_far, sp.score_scale, sp.softcap = s.bias_rows, s.bias_far, s.score_scale, s.softcap
-        sp.sink, sp.gate, sp.qkv_bias, sp.qk_norm = int(s.sink), int(s.gate), int(s.qkv_bias), int(s.qk_norm)
+        sp.sink = 2 if (s.sink and s.sink_learned) else int(s.sink)
+        sp.gate = 2 if (s.gate and s.gate_per_head) else int(s.gate)
+        sp.qkv_bias, sp.qk_norm = int(s.qkv_bias), int(s.qk_norm)
+        sp.value_from_key, sp.head_temp, sp.head_mix, sp.conv_taps = int(s.value_from_key), int(s.head_temp), int(s.head_mix), int(s.conv_taps)
         ff_kind = s.ff_kind if s.ff_dim > 0 else "none"
         sp.ff_kind, sp.ff_dim, sp.ff_act = native.FF_KINDS[ff_kind], s.ff_dim, native.ACTIVATIONS[s.ff_act]
         sp.ff_experts, sp.ff_top = s.ff_experts, s.ff_top

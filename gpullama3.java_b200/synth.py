@@ -542,4 +542,86 @@ def latusun_model(cfg: dict, weights: dict, context_length: int):
     return loader.Model(None, config, "LATUSUN", tensors)
 
 
+# ---- Lerosun: seeded synthetic models ------------------------------------------------------------------------------------
+def lerosun_attention(heads: int, kv_heads: int, key_dim: int, window: int, ff: int | None, rot_dims: int | None = None, base: float = 10000.0,
+                      scale: float | None = None) -> dict:
+    """A sliding-window attention entry of config.json's "layers" (the values are the keys, so vdim = dim; ff = None: no feed-forward)."""
+    return {"type": "attention",
+            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": key_dim, "vdim": key_dim, "mask": {"size": window},
+                      "rot": {"dims": key_dim // 2 // 2 * 2 if rot_dims is None else rot_dims, "base": float(base)},
+                      "scale": float(key_dim ** -0.5 if scale is None else scale)},
+            "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+def lerosun_delta(heads: int, kv_heads: int, key_dim: int, value_dim: int, taps: int, ff: int | None) -> dict:
+    """A gated-delta-rule entry of config.json's "layers"."""
+    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": key_dim, "vdim": value_dim, "conv": taps},
+            "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+def lerosun_config(width: int, vocab: int, layers: list, loop: tuple | None = None, eps: float = 1e-5) -> dict:
+    cfg = {"architecture": "Lerosun", "width": width, "vocab": vocab, "norm": {"eps": float(eps)}, "layers": layers}
+    if loop is not None:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def lerosun_weights(cfg: dict, seed: int = 0) -> dict:
+    """name -> float32 array in the shapes the loader expects (linear weights [out][in], norm weights 0-d); BF16-representable values."""
+    from .safetensors import bf16_bits, bf16_to_f32
+
+    rng = np.random.default_rng(seed)
+    E, V = cfg["width"], cfg["vocab"]
+    w = {}
+
+    def mat(o, i, gain=1.0):
+        return (rng.standard_normal((o, i)) * gain / np.sqrt(i)).astype(np.float32)
+
+    def vec(n, mean=0.0, std=1.0):
+        return (mean + std * rng.standard_normal(n)).astype(np.float32)
+
+    def num(mean=1.0, std=0.2):
+        return np.asarray(mean + std * rng.standard_normal(), dtype=np.float32)
+
+    w["embed"] = (rng.standard_normal((V, E)) * 0.1).astype(np.float32)
+    w["embed.norm"], w["final.norm"] = num(), num()
+    w["head"] = mat(V, E)
+    for i, lc in enumerate(cfg["layers"]):
+        m, p = lc["mixer"], f"l{i}."
+        H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        w[p + "norm1"], w[p + "ls1"] = num(), vec(E, 0.6, 0.2)
+        if lc["type"] == "attention":
+            w[p + "mix.q"], w[p + "mix.q.b"] = mat(H * dk, E, 2.0), vec(H * dk, 0.0, 0.2)
+            w[p + "mix.k"], w[p + "mix.k.b"] = mat(G * dk, E, 2.0), vec(G * dk, 0.0, 0.2)
+            w[p + "mix.talk"] = (np.eye(H) + 0.3 * rng.standard_normal((H, H))).astype(np.float32)
+            w[p + "mix.temp"], w[p + "mix.sink"] = vec(H, 1.0, 0.3), vec(H, 0.0, 1.0)
+            w[p + "mix.g"] = mat(H, E, 2.0)
+            w[p + "mix.o"] = mat(E, H * dv)
+        else:
+            K = m["conv"]
+            for n, rows in (("q", G * dk), ("k", G * dk), ("v", H * dv)):
+                w[p + "mix." + n] = mat(rows, E, 2.0)
+                w[p + "mix." + n + ".conv"] = (rng.standard_normal((rows, K)) * 0.6).astype(np.float32)
+            w[p + "mix.b"], w[p + "mix.a"] = mat(H, E, 2.0), mat(H, E, 2.0)
+            w[p + "mix.A_log"], w[p + "mix.dt_bias"] = vec(H, -1.0, 0.7), vec(H, 0.0, 0.7)
+            w[p + "mix.norm"] = vec(dv, 1.0, 0.2)
+            w[p + "mix.g"] = mat(H * dv, E, 2.0)
+            w[p + "mix.o"] = mat(E, H * dv)
+        if lc["mlp"] is not None:
+            F = lc["mlp"]["ff"]
+            w[p + "norm2"], w[p + "ls2"] = num(), vec(E, 0.6, 0.2)
+            w[p + "mlp.gate"], w[p + "mlp.up"], w[p + "mlp.down"] = mat(F, E, 1.5), mat(F, E, 1.5), mat(E, F, 1.5)
+    return {k: bf16_to_f32(bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
+
+
+def lerosun_model(cfg: dict, weights: dict, context_length: int):
+    """In-memory loader.Model (benchmarks and tests: synthetic weights never touch the disk)."""
+    from . import loader
+    from .safetensors import bf16_bits
+
+    tensors = {k: (loader.GGML_BF16, tuple(reversed(v.shape)), bf16_bits(v).view(np.uint8).reshape(-1)) for k, v in weights.items()}
+    config = loader.lerosun_configuration(cfg, {k: v.shape for k, v in weights.items()}, context_length)
+    return loader.Model(None, config, "LEROSUN", tensors)
+
+
 write_model_dir = write_pibidra_dir  # config.json + model.safetensors of any layered design

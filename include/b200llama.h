@@ -50,6 +50,12 @@ extern "C" {
                              * feed-forward a sigmoid-routed mixture of gated SiLU experts whose routing weight scales the expert's input,
                              * and the logits end in a tanh cap */
 
+#define B200_ARCH_LEROSUN 5 /* a layered design: pre-norm blocks x += s1 * mixer(R x); x += s2 * ff(R x) with RMS norms that carry ONE number as
+                             * weight and per-coordinate layer scales s1, s2; the mixer is either a sliding-window attention (partial rotation,
+                             * values = the unrotated keys, a per-head temperature, scores mixed over the heads before the softmax, a learned
+                             * sink logit per head, one sigmoid gate per head) or a gated delta rule (a recurrent state matrix per head behind
+                             * short causal convolutions); a gated ReLU feed-forward; a block of layers may run several passes */
+
 /* GGML tensor type ids accepted for weights (tensor/GGMLType.java:5-20) */
 #define B200_GGML_F32 0
 #define B200_GGML_F16 1
@@ -116,6 +122,12 @@ int b200_plan_create(const b200_config *cfg, const b200_tensor *tensors, int32_t
                                        * latent; score = score_scale * (<q_u, k> + <rot q_r, rot shared>); causal softmax; optional sigmoid
                                        * gate; Wo.  The cache holds [latent | rotated shared key part] per position; the kernels fold Wuk into
                                        * the query and Wuv into the output, so keys and values are never expanded */
+#define B200_MIXER_GATED_DELTA 3 /* q, k (kv_heads x key_dim) and v (heads x value_dim) pass a causal convolution of conv_taps taps per channel
+                                  * ("<layer>.mix.{q,k,v}.conv" [channels][taps], last tap = the current token) and SiLU; q and k become unit vectors
+                                  * per head (x / sqrt(|x|^2 + 1e-6)), q times key_dim^-1/2; beta = sigmoid(W_b a), gamma = exp(-exp(A_log) *
+                                  * softplus(W_a a + dt_bias)) per head; per head S <- gamma S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q;
+                                  * y = o / rms(o) * w ("<layer>.mix.norm" [value_dim]) * silu(W_g a); W_o.  The state S [key_dim][value_dim] per
+                                  * head (FP32, zero at position 0) and the last conv_taps - 1 convolution inputs are carried between calls */
 #define B200_FF_NONE 0
 #define B200_FF_DENSE_GATED 1 /* down(act(gate x) * (up x)) */
 #define B200_FF_MOE 2         /* sum over the ff_top experts with the largest router scores of expert_e(s_e * x), expert = FF_DENSE_GATED without
@@ -123,9 +135,13 @@ int b200_plan_create(const b200_config *cfg, const b200_tensor *tensors, int32_t
 #define B200_ROPE_HALF 0        /* pair (i, i + rot_dims / 2) */
 #define B200_ROPE_INTERLEAVED 1 /* pair (2i, 2i + 1) */
 #define B200_BLOCK_SANDWICH 0 /* x += N(mixer(N x)); x += N(ff(N x)) with (1 + w)-weighted RMS norms (Pibidra) */
+#define B200_BLOCK_PRENORM 2  /* x += s1 * mixer(R(x; g1)); x += s2 * ff(R(x; g2)): R = RMS norm times ONE number ("<layer>.norm1", a scalar tensor),
+                               * s = a vector ("<layer>.ls1"); the embedding output passes R(.; "embed.norm"); a loop block repeats without a
+                               * prologue (nothing is re-added between passes) */
 #define B200_BLOCK_PARALLEL 1 /* x += residual_mult * (mixer(LN1 x) + ff(LN2 x)), layer norms with weight and bias ("<layer>.norm1", ".norm1.b", ...) */
 #define B200_ACT_GELU_TANH 0
 #define B200_ACT_SILU 1
+#define B200_ACT_RELU 2
 #define B200_COMPUTE_BF16 0 /* prefill GEMM operands rounded to BF16, FP32 accumulation; decode FP32 activations x BF16 weights */
 #define B200_COMPUTE_F32 1  /* every product in true FP32 (BF16 weights widen exactly) */
 
@@ -141,8 +157,10 @@ typedef struct b200_layer_spec {
     float bias_far;
     float score_scale;  /* multiplies <q, k> (not the bias) */
     float softcap;      /* score <- softcap * tanh(score / softcap); <= 0: none */
-    int32_t sink;       /* 1: softmax denominator 1 + sum exp (an extra zero logit without a value) */
-    int32_t gate;       /* 1: heads * sigmoid(W_g h) before the output projection ("<layer>.mix.g") */
+    int32_t sink;       /* 1: softmax denominator 1 + sum exp (an extra zero logit without a value); 2: exp(z_h) + sum exp with a learned
+                           logit per head ("<layer>.mix.sink" [heads]) */
+    int32_t gate;       /* 1: heads * sigmoid(W_g h) before the output projection ("<layer>.mix.g" [heads * value_dim][width]); 2: ONE sigmoid
+                           gate per head ("<layer>.mix.g" [heads][width]) */
     int32_t qkv_bias;   /* 1: "<layer>.mix.{q,k,v}.b" */
     int32_t qk_norm;    /* 1: one RMS norm over the whole q projection and one over the whole k projection, weights used as stored */
     int32_t ff_kind;    /* B200_FF_* */
@@ -160,10 +178,17 @@ typedef struct b200_layer_spec {
     /* B200_FF_MOE (ff_dim = width of one expert) */
     int32_t ff_experts;
     int32_t ff_top;
+    /* B200_MIXER_WINDOW_ATTENTION, each switchable on its own.  rope_dims > 0 rotates the first rope_dims entries of every query and key
+     * head (rope_layout, rope_base as above; no frequency blending) */
+    int32_t value_from_key; /* 1: no W_v; the values are the keys as projected (with their bias), BEFORE the rotation; value_dim == key_dim */
+    int32_t head_temp;      /* 1: head h's score is multiplied by "<layer>.mix.temp"[h] */
+    int32_t head_mix;       /* 1: score_h <- sum_m T[h][m] score_m over the query heads before cap, bias and softmax ("<layer>.mix.talk" [heads][heads]) */
+    /* B200_MIXER_GATED_DELTA */
+    int32_t conv_taps;      /* taps of the causal convolution (>= 1) */
 } b200_layer_spec;
 
 typedef struct b200_layered_config {
-    int32_t arch;           /* B200_ARCH_PIBIDRA, B200_ARCH_LATUSUN */
+    int32_t arch;           /* B200_ARCH_PIBIDRA, B200_ARCH_LATUSUN, B200_ARCH_LEROSUN */
     int32_t width;
     int32_t vocab_size;
     int32_t n_layers;
@@ -270,7 +295,8 @@ int b200_decode_sequence(b200_plan *plan, const int32_t *tokens, int32_t n, int3
 int b200_kv_reset(b200_plan *plan);
 
 /* Test/diagnostic read-back of a named device buffer into host memory.  Names:
- * "x","xb","q","k","v","hb","logits","key_cache","value_cache","xq","xs".  `layer` selects the
+ * "x","xb","q","k","v","hb","logits","key_cache","value_cache","xq","xs"; layered plans with a gated-delta run: "delta_state"
+ * ([heads][key_dim][value_dim]) and "conv_state" (the ring of convolution inputs).  `layer` selects the
  * layer for the KV caches (ignored otherwise).  Copies min(bytes, buffer size).  Layered plans: `layer` is the layer RUN;
  * a latent-attention run has ONE cache, "key_cache" = rows [latent | rotated shared key part], and no "value_cache". */
 int b200_read_buffer(b200_plan *plan, const char *name, int32_t layer, void *dst, size_t bytes);
