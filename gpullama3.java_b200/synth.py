@@ -589,10 +589,10 @@ def lerosun_weights(cfg: dict, seed: int = 0) -> dict:
     for i, lc in enumerate(cfg["layers"]):
         m, p = lc["mixer"], f"l{i}."
         H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-        w[p + "norm1"], w[p + "ls1"] = num(), vec(E, 0.6, 0.2)
+        w[p + "norm1"], w[p + "ls1"] = num(), vec(E, 0.5, 0.2)
         if lc["type"] == "attention":
-            w[p + "mix.q"], w[p + "mix.q.b"] = mat(H * dk, E, 2.0), vec(H * dk, 0.0, 0.2)
-            w[p + "mix.k"], w[p + "mix.k.b"] = mat(G * dk, E, 2.0), vec(G * dk, 0.0, 0.2)
+            w[p + "mix.q"], w[p + "mix.q.b"] = mat(H * dk, E, 1.5), vec(H * dk, 0.0, 0.2)
+            w[p + "mix.k"], w[p + "mix.k.b"] = mat(G * dk, E, 1.5), vec(G * dk, 0.0, 0.2)
             w[p + "mix.talk"] = (np.eye(H) + 0.3 * rng.standard_normal((H, H))).astype(np.float32)
             w[p + "mix.temp"], w[p + "mix.sink"] = vec(H, 1.0, 0.3), vec(H, 0.0, 1.0)
             w[p + "mix.g"] = mat(H, E, 2.0)
@@ -609,8 +609,8 @@ def lerosun_weights(cfg: dict, seed: int = 0) -> dict:
             w[p + "mix.o"] = mat(E, H * dv)
         if lc["mlp"] is not None:
             F = lc["mlp"]["ff"]
-            w[p + "norm2"], w[p + "ls2"] = num(), vec(E, 0.6, 0.2)
-            w[p + "mlp.gate"], w[p + "mlp.up"], w[p + "mlp.down"] = mat(F, E, 1.5), mat(F, E, 1.5), mat(E, F, 1.5)
+            w[p + "norm2"], w[p + "ls2"] = num(), vec(E, 0.5, 0.2)
+            w[p + "mlp.gate"], w[p + "mlp.up"], w[p + "mlp.down"] = mat(F, E), mat(F, E), mat(E, F)
     return {k: bf16_to_f32(bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
 
 
