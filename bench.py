@@ -263,6 +263,59 @@ def compare_latusun(pkg, lb, local: int, steps: int, warmup: int, sizes):
             "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "tensor_tflops": burst, "tensor_source": t_src}, "sizes": out}
 
 
+# ---- --compare lerosun: the pre-norm hybrid (windowed attention + gated delta rule) beside the closest existing model (Pibidra) -----
+# Both are layered plans with BF16 weights, an FP32 residual, window rings and the same projection kernels.  Equal size = same width,
+# feed-forward width, heads, key/value heads, head size, window, vocabulary and number of layer runs; the Pibidra layers are all
+# attention, the Lerosun layers alternate delta / attention / attention / delta with the two attention layers looped twice.
+LEROSUN_SIZES = {
+    # name: (width, ff, attention heads, key/value heads, head size, window, delta value heads, delta q/k heads, delta key size, delta value size, taps, vocab)
+    # (the head-mixed attention reads key rows of key/value heads x head size = 128 / 256 with values of 64 / 128: instances of the tensor-core attention)
+    "small": (1024, 4096, 16, 2, 64, 1024, 8, 4, 64, 128, 4, 32768),
+    "1b-like": (2048, 8192, 16, 2, 128, 1024, 16, 8, 128, 128, 4, 32768),
+}
+
+
+def compare_lerosun(pkg, lb, local: int, steps: int, warmup: int, sizes):
+    hbm, hbm_src = peaks()
+    burst, sustained, t_src = tensor_peak()
+    S = pkg.synth
+    out = {}
+    for name in sizes:
+        E, F, H, G, hs, Wn, DH, DG, ddk, ddv, taps, V = LEROSUN_SIZES[name]
+        depth, n_pp = 64, 512
+        ctx = max(depth + steps + warmup + 8, n_pp + 8)
+        toks = np.asarray(lb.synthetic_tokens(V, ctx), dtype=np.int32)
+        att, dlt = S.lerosun_attention(H, G, hs, Wn, F, rot_dims=hs // 2), S.lerosun_delta(DH, DG, ddk, ddv, taps, F)
+        cfg = S.lerosun_config(E, V, [dlt, att, att, dlt], loop=(1, 3, 2))
+        order = [dlt, att, att, att, att, dlt]  # the six layer runs
+        w = S.lerosun_weights(cfg, 1234)
+        att_w = (H * hs + G * hs + H) * E + H * hs * E + 3 * F * E
+        dlt_w = (2 * DG * ddk + 2 * DH * ddv + 2 * DH) * E + DH * ddv * E + 3 * F * E
+        streamed = sum(att_w if lc["type"] == "attention" else dlt_w for lc in order)
+        pairs = sum(min(i + 1, Wn) for i in range(n_pp))
+        mix_mac = sum((H * 2 * hs * pairs) if lc["type"] == "attention" else (3 * DH * ddk * ddv * n_pp) for lc in order)  # scores + values | S^T k, k u^T, S^T q
+        plan = pkg.B200MasterPlan.initialize_plan(S.lerosun_model(cfg, w, ctx), prefill_batch_size=n_pp, device=local, compute="bfloat16")
+        row = {"lerosun_bfloat16": _layered_leg(plan, toks, depth, warmup, steps, n_pp, hbm, burst, 2 * (streamed + V * E), 2.0 * streamed * n_pp + 2.0 * mix_mac,
+                                                ((0, "gate_up"), (1, "down"), (2, "fused_projection"), (3, "mixer_out"), (4, "classifier")))}
+        plan.free()
+        del w
+        runs = len(order)
+        pcfg = S.pibidra_config(E, V, [S.pibidra_layer(H, G, hs, hs, Wn, F, bias_max=float(Wn)) for _ in range(runs)])
+        pw = S.pibidra_weights(pcfg, 1234, bias_rows=32)
+        per = (2 * H * hs + 2 * G * hs) * E + H * hs * E + 3 * F * E
+        plan = pkg.B200MasterPlan.initialize_plan(S.pibidra_model(pcfg, pw, ctx), prefill_batch_size=n_pp, device=local, compute="bfloat16")
+        row["pibidra_bfloat16"] = _layered_leg(plan, toks, depth, warmup, steps, n_pp, hbm, burst, 2 * (runs * per + V * E), 2.0 * runs * per * n_pp + 2.0 * runs * H * 2 * hs * pairs,
+                                               ((0, "gate_up"), (1, "down"), (2, "qkvg"), (3, "attn_out"), (4, "classifier")))
+        plan.free()
+        del pw
+        row["config"] = {"width": E, "ff": F, "attention": f"{H} heads, {G} key/value heads of {hs}, window {Wn}", "delta": f"{DH} value heads of {ddv}, {DG} query/key heads of {ddk}, {taps} taps",
+                         "vocab": V, "layer_runs": runs, "order": "delta, (attention, attention) x 2, delta", "closest": f"Pibidra: {runs} attention layers of the same heads and window",
+                         "decode": f"tg{steps} from depth {depth + warmup}", "prefill": f"pp{n_pp} in one chunk from depth 0"}
+        out[name] = row
+    return {"metric": "lerosun_vs_closest_model", "unit": "tok/s", "data": "synthetic", "dtype": "bf16 weights, f32 accumulate",
+            "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "tensor_tflops": burst, "tensor_source": t_src}, "sizes": out}
+
+
 class ClockSampler:
     """nvidia-smi clocks/throttle reasons sampled DURING the timed region."""
     Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
@@ -378,10 +431,10 @@ def main():
     ap.add_argument("--depth", type=int, default=-1, help="LlamaBench -d: KV positions filled before the timed steps (default: the warm-up steps)")
     ap.add_argument("--workload", default=WORKLOAD, choices=["llama-3-8b", "llama-3-70b", "llama-3.2-1b", "qwen3-4b"],
                     help="shape of the synthetic model (default: the BASELINE headline, Llama-3-8B; 70B is BASELINE config 5, meant for --gpus 2/4/8)")
-    ap.add_argument("--compare", default=None, choices=["pibidra", "latusun"],
+    ap.add_argument("--compare", default=None, choices=["pibidra", "latusun", "lerosun"],
                     help="instead of the headline workload: decode and prefill throughput of a layered design beside its closest existing model "
-                         "at equal sizes (pibidra: the FP16 Qwen3 plan; latusun: the Pibidra plan), with per-kernel rooflines; one JSON line")
-    ap.add_argument("--compare-sizes", default=None, help="comma-separated size names (pibidra: 1b-like,8b-like; latusun: small,lite-like)")
+                         "at equal sizes (pibidra: the FP16 Qwen3 plan; latusun, lerosun: the Pibidra plan), with per-kernel rooflines; one JSON line")
+    ap.add_argument("--compare-sizes", default=None, help="comma-separated size names (pibidra: 1b-like,8b-like; latusun: small,lite-like; lerosun: small,1b-like)")
     args = ap.parse_args()
     K, W = args.steps, max(args.warmup, 3)
     if args.compare:
@@ -392,7 +445,9 @@ def main():
         pkg = ge.import_package()
         sampler = ClockSampler(local)
         sampler.start()
-        if args.compare == "latusun":
+        if args.compare == "lerosun":
+            line = compare_lerosun(pkg, pkg.llama_bench, local, min(K, 64), W, (args.compare_sizes or "small,1b-like").split(","))
+        elif args.compare == "latusun":
             line = compare_latusun(pkg, pkg.llama_bench, local, min(K, 64), W, (args.compare_sizes or "small,lite-like").split(","))
         else:
             line = compare_layered(pkg, pkg.llama_bench, local, min(K, 64), W, (args.compare_sizes or "1b-like,8b-like").split(","))

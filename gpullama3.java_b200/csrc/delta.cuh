@@ -10,8 +10,9 @@
 //                       matrix the query is only scaled by its head's temperature;
 //   * k_delta_prep      gated delta rule, everything in front of the recurrence: causal convolution of the q | k | v channels over
 //                       a ring of earlier inputs, SiLU, unit vectors per q / k head, beta = sigmoid, decay = exp(-exp(A) softplus);
-//   * k_delta_rule      the recurrence S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, one thread per state column,
-//                       rows of a chunk in sequence, the state tile resident in shared memory for the whole chunk;
+//   * k_delta_rule_reg  the recurrence S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q with the state in registers: eight
+//                       lanes share a state column, the rows of a chunk run in sequence, columns in parallel over warps and CTAs;
+//   * k_delta_rule      the same for key sizes above 128: one thread per state column, the state tile in shared memory;
 //   * k_head_norm_gate  per-head RMS norm of the read-out, weight, SiLU gate.
 // Rotation, scores, decays, gates, unit norms and the state are FP32 in both compute modes; fmaf is explicit because the
 // translation unit is compiled with -fmad=false.
@@ -30,55 +31,64 @@ struct RopeMixArgs {
     int ring;                    // position j lives in slot j % ring
 };
 
-// One CTA per row.  P row: [q: heads*dk | k: kv_heads*dk | v: kv_heads*dv (absent with value_from_key) | ...]; q and k are
-// rotated in place.  Q row (ldq): heads * (talk ? kv_heads * dk : dk) entries.
-__global__ void __launch_bounds__(256) k_rope_mix_prep(float *__restrict__ P, int ldp, RopeMixArgs a, const float *__restrict__ bias, float *__restrict__ Q, int ldq,
-                                                       float *__restrict__ kc, float *__restrict__ vc, bf16 *__restrict__ kc16, bf16 *__restrict__ vc16,
-                                                       const StepState *__restrict__ st) {
+// grid (rows, heads + 1), 128 threads; dynamic shared memory: heads * dk floats.  P row: [q: heads*dk | k: kv_heads*dk | v: kv_heads*dv
+// (absent with value_from_key) | ...].  CTA (r, h < heads) biases and rotates ALL query heads of the row into shared memory (every
+// mixed query needs them all; the row in P stays as projected) and writes head h's query: heads * (talk ? kv_heads * dk : dk) entries
+// per Q row (ldq).  CTA (r, heads) owns the key side: bias, value row = unrotated key (or the value projection), rotation, key row.
+#define ROPE_MIX_THREADS 128
+__global__ void __launch_bounds__(ROPE_MIX_THREADS) k_rope_mix_prep(const float *__restrict__ P, int ldp, RopeMixArgs a, const float *__restrict__ bias, float *__restrict__ Q, int ldq,
+                                                                    float *__restrict__ kc, float *__restrict__ vc, bf16 *__restrict__ kc16, bf16 *__restrict__ vc16,
+                                                                    const StepState *__restrict__ st) {
+    extern __shared__ __align__(16) float xs[];
     const int r = blockIdx.x, tid = threadIdx.x;
-    const int qd = a.heads * a.dk, kd = a.kv_heads * a.dk, vd = a.kv_heads * a.dv, pv = a.value_from_key ? 0 : vd;
-    float *q = P + (size_t)r * ldp, *k = q + qd;
-    const float *v = a.value_from_key ? k : k + kd;
-    const int pos = st->pos + r, slot = pos % a.ring;
-    if (bias) {
-        for (int i = tid; i < qd + kd + pv; i += 256) q[i] += bias[i];
-        __syncthreads();
-    }
-    for (int i = tid; i < vd; i += 256) {
-        vc[(size_t)slot * vd + i] = v[i];
-        if (vc16) vc16[(size_t)slot * vd + i] = __float2bfloat16_rn(v[i]);
-    }
-    if (a.rope_dims > 0) {
-        __syncthreads(); // the values above are read from the unrotated keys
-        const int half = a.rope_dims / 2;
-        const float *cs = a.cs + (size_t)pos * half * 2;
-        for (int e = tid; e < (a.heads + a.kv_heads) * half; e += 256) {
-            const int hd = e / half, i = e % half;
-            int u, w;
-            rope_pair_index(i, a.rope_dims, a.rope_layout, u, w);
-            float *x = q + (size_t)hd * a.dk; // the key heads follow the query heads in the row
-            const float co = cs[2 * i], si = cs[2 * i + 1];
-            const float xu = x[u], xw = x[w];
-            x[u] = fmaf(xu, co, -(xw * si));
-            x[w] = fmaf(xw, co, xu * si);
+    const int qd = a.heads * a.dk, kd = a.kv_heads * a.dk, vd = a.kv_heads * a.dv;
+    const float *p = P + (size_t)r * ldp;
+    const int pos = st->pos + r, slot = pos % a.ring, half = a.rope_dims / 2;
+    const float *cs = a.cs + (size_t)pos * half * 2;
+    const bool key_side = (int)blockIdx.y == a.heads;
+    // this CTA's vectors, biased: all query heads, or all key heads
+    const int off = key_side ? qd : 0, len = key_side ? kd : qd, nh = key_side ? a.kv_heads : a.heads;
+    for (int i = tid; i < len; i += ROPE_MIX_THREADS) xs[i] = p[off + i] + (bias ? bias[off + i] : 0.0f);
+    __syncthreads();
+    if (key_side) {
+        for (int i = tid; i < vd; i += ROPE_MIX_THREADS) {
+            const float v = a.value_from_key ? xs[i] : p[qd + kd + i] + (bias ? bias[qd + kd + i] : 0.0f);
+            vc[(size_t)slot * vd + i] = v;
+            if (vc16) vc16[(size_t)slot * vd + i] = __float2bfloat16_rn(v);
         }
+        __syncthreads(); // the values above are the unrotated keys
+    }
+    for (int e = tid; e < nh * half; e += ROPE_MIX_THREADS) {
+        const int hd = e / half, i = e % half;
+        int u, w;
+        rope_pair_index(i, a.rope_dims, a.rope_layout, u, w);
+        float *x = xs + (size_t)hd * a.dk;
+        const float co = cs[2 * i], si = cs[2 * i + 1];
+        const float xu = x[u], xw = x[w];
+        x[u] = fmaf(xu, co, -(xw * si));
+        x[w] = fmaf(xw, co, xu * si);
     }
     __syncthreads();
-    for (int i = tid; i < kd; i += 256) {
-        kc[(size_t)slot * kd + i] = k[i];
-        if (kc16) kc16[(size_t)slot * kd + i] = __float2bfloat16_rn(k[i]);
+    if (key_side) {
+        for (int i = tid; i < kd; i += ROPE_MIX_THREADS) {
+            kc[(size_t)slot * kd + i] = xs[i];
+            if (kc16) kc16[(size_t)slot * kd + i] = __float2bfloat16_rn(xs[i]);
+        }
+        return;
     }
-    float *qo = Q + (size_t)r * ldq;
+    const int h = blockIdx.y;
     if (a.talk) {
-        const int group = a.heads / a.kv_heads, row = kd;
-        for (int e = tid; e < a.heads * row; e += 256) {
-            const int h = e / row, c = e % row, kv = c / a.dk, d = c % a.dk;
+        const int group = a.heads / a.kv_heads;
+        float *qo = Q + (size_t)r * ldq + (size_t)h * kd;
+        for (int c = tid; c < kd; c += ROPE_MIX_THREADS) {
+            const int kv = c / a.dk, d = c % a.dk;
             float s = 0.0f;
-            for (int m = kv * group; m < (kv + 1) * group; m++) s = fmaf(a.talk[h * a.heads + m] * (a.temp ? a.temp[m] : 1.0f), q[(size_t)m * a.dk + d], s);
-            qo[e] = s;
+            for (int m = kv * group; m < (kv + 1) * group; m++) s = fmaf(a.talk[h * a.heads + m] * (a.temp ? a.temp[m] : 1.0f), xs[(size_t)m * a.dk + d], s);
+            qo[c] = s;
         }
     } else {
-        for (int e = tid; e < qd; e += 256) qo[e] = a.temp ? q[e] * a.temp[e / a.dk] : q[e];
+        float *qo = Q + (size_t)r * ldq + (size_t)h * a.dk;
+        for (int d = tid; d < a.dk; d += ROPE_MIX_THREADS) qo[d] = a.temp ? xs[(size_t)h * a.dk + d] * a.temp[h] : xs[(size_t)h * a.dk + d];
     }
 }
 
@@ -97,17 +107,35 @@ struct DeltaArgs {
 // Row layout of the prepared buffer D (ldd): [q unit / sqrt(dk) | k unit | v | beta: heads | decay: heads]
 __host__ __device__ inline int delta_channels(const DeltaArgs &a) { return 2 * a.kv_heads * a.dk + a.heads * a.dv; }
 
-// One CTA per row; dynamic shared memory: delta_channels floats.  A row at position p reads the inputs of positions p - taps + 1
-// .. p: from the rows of this launch where they belong to it, else from the ring (written by earlier launches; positions before
-// the start of the sequence count as zero).  Every row leaves its own input in the ring.
-__global__ void __launch_bounds__(256) k_delta_prep(const float *__restrict__ P, int ldp, DeltaArgs a, float *__restrict__ cstate, float *__restrict__ D, int ldd,
-                                                    const StepState *__restrict__ st) {
+// grid (rows, 2 * kv_heads + heads + 1), 128 threads; dynamic shared memory: max(dk, dv) floats.  CTA (r, u) owns one unit of the row:
+// a query head, a key head (convolution, SiLU, unit vector), a value head (convolution, SiLU), or -- the last unit -- beta and decay
+// of all heads.  A row at position p reads the inputs of positions p - taps + 1 .. p: from the rows of this launch where they belong
+// to it, else from the ring (written by earlier launches; positions before the start of the sequence count as zero).  Every unit
+// leaves its own input channels in the ring.
+#define DELTA_PREP_THREADS 128
+__global__ void __launch_bounds__(DELTA_PREP_THREADS) k_delta_prep(const float *__restrict__ P, int ldp, DeltaArgs a, float *__restrict__ cstate, float *__restrict__ D, int ldd,
+                                                                   const StepState *__restrict__ st) {
     extern __shared__ __align__(16) float row[];
-    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float red[32];
+    const int r = blockIdx.x, u = blockIdx.y, tid = threadIdx.x;
     const int C = delta_channels(a), qk = a.kv_heads * a.dk;
     const int pos = st->pos + r;
     const float *p = P + (size_t)r * ldp;
-    for (int c = tid; c < C; c += 256) {
+    float *d = D + (size_t)r * ldd;
+    if (u == 2 * a.kv_heads + a.heads) {
+        for (int h = tid; h < a.heads; h += DELTA_PREP_THREADS) {
+            d[C + h] = 1.0f / (1.0f + expf(-p[C + h]));
+            const float z = p[C + a.heads + h] + a.dt_bias[h];
+            const float sp = fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z)));
+            d[C + a.heads + h] = expf(-expf(a.a_log[h]) * sp);
+        }
+        return;
+    }
+    const bool unit_vec = u < 2 * a.kv_heads;
+    const int c0 = unit_vec ? u * a.dk : 2 * qk + (u - 2 * a.kv_heads) * a.dv, len = unit_vec ? a.dk : a.dv;
+    float ss = 0.0f;
+    for (int i = tid; i < len; i += DELTA_PREP_THREADS) {
+        const int c = c0 + i;
         float acc = 0.0f;
         for (int m = 0; m < a.taps; m++) {
             const int back = a.taps - 1 - m;
@@ -116,27 +144,15 @@ __global__ void __launch_bounds__(256) k_delta_prep(const float *__restrict__ P,
             acc = fmaf(a.conv_w[(size_t)c * a.taps + m], x, acc);
         }
         cstate[(size_t)(pos % a.cring) * C + c] = p[c];
-        row[c] = acc / (1.0f + expf(-acc));
+        const float y = acc / (1.0f + expf(-acc));
+        if (unit_vec) { row[i] = y; ss = fmaf(y, y, ss); }
+        else d[c] = y;
     }
-    __syncthreads();
-    float *d = D + (size_t)r * ldd;
-    // q heads then k heads: one warp per head
-    for (int hd = warp; hd < 2 * a.kv_heads; hd += 8) {
-        const float *x = row + (size_t)hd * a.dk;
-        float ss = 0.0f;
-        for (int i = lane; i < a.dk; i += 32) ss = fmaf(x[i], x[i], ss);
-        ss = warp_sum(ss);
-        float inv = 1.0f / sqrtf(ss + a.unit_eps);
-        if (hd < a.kv_heads) inv *= 1.0f / sqrtf((float)a.dk);
-        for (int i = lane; i < a.dk; i += 32) d[(size_t)hd * a.dk + i] = x[i] * inv;
-    }
-    for (int c = 2 * qk + tid; c < C; c += 256) d[c] = row[c];
-    for (int h = tid; h < a.heads; h += 256) {
-        d[C + h] = 1.0f / (1.0f + expf(-p[C + h]));
-        const float z = p[C + a.heads + h] + a.dt_bias[h];
-        const float sp = fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z)));
-        d[C + a.heads + h] = expf(-expf(a.a_log[h]) * sp);
-    }
+    if (!unit_vec) return;
+    ss = block_sum(ss, red);
+    float inv = 1.0f / sqrtf(ss + a.unit_eps);
+    if (u < a.kv_heads) inv *= 1.0f / sqrtf((float)a.dk);
+    for (int i = tid; i < len; i += DELTA_PREP_THREADS) d[c0 + i] = row[i] * inv;
 }
 
 // grid (heads, column tiles), DELTA_COLS threads: thread j owns column j of the head's state S [dk][dv]; the tile S[:, cols] stays
@@ -186,6 +202,80 @@ __global__ void __launch_bounds__(DELTA_COLS) k_delta_rule(const float *__restri
     }
     if (live)
         for (int i = 0; i < dk; i++) Sg[(size_t)i * dv + j] = Ss[i * DELTA_COLS + tid];
+}
+
+// The same recurrence with the state in REGISTERS (key sizes up to 8 * R, R = 1, 2, 4, 8 or 16): grid (heads, column tiles of DR_COLS),
+// 256 threads.  A column of S is shared by DR_SLICES = 8 neighbouring lanes, lane s holding rows s, s + 8, s + 16, ...; the two
+// products S^T k and S^T q are R multiply-adds per lane and a three-step shuffle.  Columns are independent, a warp owns four of them
+// completely, so the only block-wide step is staging DR_TB tokens of k, q, v, beta and decay in shared memory at a time (and
+// writing their read-outs back coalesced).  The state buffer is private to this kernel: [head][tile][R][thread].
+#define DR_COLS 32
+#define DR_SLICES 8
+#define DR_THREADS 256
+#define DR_TB 16
+__host__ __device__ inline int delta_reg_rows(int dk) { return dk <= 8 ? 1 : dk <= 16 ? 2 : dk <= 32 ? 4 : dk <= 64 ? 8 : dk <= 128 ? 16 : 0; } // 0: the shared-memory kernel
+__host__ __device__ inline size_t delta_state_floats(int heads, int dk, int dv) {
+    const int R = delta_reg_rows(dk);
+    return R ? (size_t)heads * ((dv + DR_COLS - 1) / DR_COLS) * R * DR_THREADS : (size_t)heads * dk * dv;
+}
+
+template <int R>
+__global__ void __launch_bounds__(DR_THREADS) k_delta_rule_reg(const float *__restrict__ D, int ldd, DeltaArgs a, float *__restrict__ S, int n, float *__restrict__ O, int ldo,
+                                                               const StepState *__restrict__ st) {
+    constexpr int KR = DR_SLICES * R; // key rows the threads cover (>= dk; the rest multiply zeros)
+    __shared__ float ks[DR_TB][KR], qs[DR_TB][KR], vs[DR_TB][DR_COLS], os[DR_TB][DR_COLS], bd[DR_TB][2];
+    const int h = blockIdx.x, tile = blockIdx.y, j0 = tile * DR_COLS, tid = threadIdx.x, lane = tid & 31;
+    const int c = (tid >> 5) * 4 + (lane >> 3), s = lane & 7;
+    const int dk = a.dk, dv = a.dv, g = h / (a.heads / a.kv_heads), C = delta_channels(a);
+    float *Sg = S + ((size_t)h * gridDim.y + tile) * R * DR_THREADS + tid;
+    float Sr[R];
+    const bool fresh = st->pos == 0;
+#pragma unroll
+    for (int i = 0; i < R; i++) Sr[i] = fresh ? 0.0f : Sg[(size_t)i * DR_THREADS];
+    for (int t0 = 0; t0 < n; t0 += DR_TB) {
+        const int nb = n - t0 < DR_TB ? n - t0 : DR_TB;
+        for (int e = tid; e < nb * KR; e += DR_THREADS) {
+            const int t = e / KR, i = e % KR;
+            const float *d = D + (size_t)(t0 + t) * ldd;
+            ks[t][i] = i < dk ? d[(size_t)(a.kv_heads + g) * dk + i] : 0.0f;
+            qs[t][i] = i < dk ? d[(size_t)g * dk + i] : 0.0f;
+        }
+        for (int e = tid; e < nb * DR_COLS; e += DR_THREADS) {
+            const int t = e / DR_COLS, cc = e % DR_COLS;
+            vs[t][cc] = j0 + cc < dv ? D[(size_t)(t0 + t) * ldd + 2 * a.kv_heads * dk + (size_t)h * dv + j0 + cc] : 0.0f;
+        }
+        if (tid < nb * 2) bd[tid >> 1][tid & 1] = D[(size_t)(t0 + (tid >> 1)) * ldd + C + (tid & 1) * a.heads + h];
+        __syncthreads();
+        for (int t = 0; t < nb; t++) {
+            const float beta = bd[t][0], decay = bd[t][1];
+            float kr[R];
+            float rd = 0.0f;
+#pragma unroll
+            for (int i = 0; i < R; i++) { kr[i] = ks[t][i * DR_SLICES + s]; rd = fmaf(Sr[i], kr[i], rd); }
+            rd += __shfl_xor_sync(0xffffffffu, rd, 1);
+            rd += __shfl_xor_sync(0xffffffffu, rd, 2);
+            rd += __shfl_xor_sync(0xffffffffu, rd, 4);
+            const float u = beta * (vs[t][c] - decay * rd);
+            float o = 0.0f;
+#pragma unroll
+            for (int i = 0; i < R; i++) {
+                Sr[i] = fmaf(kr[i], u, decay * Sr[i]);
+                o = fmaf(Sr[i], qs[t][i * DR_SLICES + s], o);
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            if (s == 0) os[t][c] = o;
+        }
+        __syncthreads();
+        for (int e = tid; e < nb * DR_COLS; e += DR_THREADS) {
+            const int t = e / DR_COLS, cc = e % DR_COLS;
+            if (j0 + cc < dv) O[(size_t)(t0 + t) * ldo + (size_t)h * dv + j0 + cc] = os[t][cc];
+        }
+        // the next block's staging writes ks / qs / vs / bd only; os is rewritten after the barrier that follows the staging
+    }
+#pragma unroll
+    for (int i = 0; i < R; i++) Sg[(size_t)i * DR_THREADS] = Sr[i];
 }
 
 // One CTA per row, one warp per head: y = o / sqrt(mean(o^2) + eps) * w[d] * silu(gate[h][d]).

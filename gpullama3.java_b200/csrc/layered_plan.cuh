@@ -316,9 +316,21 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
             ly::DeltaArgs da{};
             da.heads = L.s.heads; da.kv_heads = L.s.kv_heads; da.dk = L.s.key_dim; da.dv = L.s.value_dim; da.taps = L.s.conv_taps; da.cring = Y.cring;
             da.conv_w = L.conv_w; da.a_log = L.a_log; da.dt_bias = L.dt_bias; da.unit_eps = 1e-6f;
-            if ((rc = launch_k(p, false, ly::k_delta_prep, dim3(n), dim3(256), (size_t)L.dC * 4, (const float *)Y.PROJ, Y.maxP, da, R.cstate, Y.DLT, Y.maxD, st))) return rc;
-            if ((rc = launch_k(p, false, ly::k_delta_rule, dim3(L.s.heads, (L.s.value_dim + DELTA_COLS - 1) / DELTA_COLS), dim3(DELTA_COLS), ly::delta_rule_smem_floats(L.s.key_dim) * 4,
-                               (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st))) return rc;
+            const int dmax = L.s.key_dim > L.s.value_dim ? L.s.key_dim : L.s.value_dim;
+            if ((rc = launch_k(p, false, ly::k_delta_prep, dim3(n, 2 * L.s.kv_heads + L.s.heads + 1), dim3(DELTA_PREP_THREADS), (size_t)dmax * 4, (const float *)Y.PROJ, Y.maxP, da, R.cstate,
+                               Y.DLT, Y.maxD, st))) return rc;
+            const dim3 rgrid(L.s.heads, (L.s.value_dim + DR_COLS - 1) / DR_COLS), rblock(DR_THREADS);
+            switch (ly::delta_reg_rows(L.s.key_dim)) {
+            case 1: rc = launch_k(p, false, ly::k_delta_rule_reg<1>, rgrid, rblock, (size_t)0, (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st); break;
+            case 2: rc = launch_k(p, false, ly::k_delta_rule_reg<2>, rgrid, rblock, (size_t)0, (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st); break;
+            case 4: rc = launch_k(p, false, ly::k_delta_rule_reg<4>, rgrid, rblock, (size_t)0, (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st); break;
+            case 8: rc = launch_k(p, false, ly::k_delta_rule_reg<8>, rgrid, rblock, (size_t)0, (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st); break;
+            case 16: rc = launch_k(p, false, ly::k_delta_rule_reg<16>, rgrid, rblock, (size_t)0, (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st); break;
+            default: // key sizes above 128: the state tile in shared memory, one thread per column
+                rc = launch_k(p, false, ly::k_delta_rule, dim3(L.s.heads, (L.s.value_dim + DELTA_COLS - 1) / DELTA_COLS), dim3(DELTA_COLS), ly::delta_rule_smem_floats(L.s.key_dim) * 4,
+                              (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st);
+            }
+            if (rc) return rc;
             if ((rc = launch_k(p, false, ly::k_head_norm_gate, dim3(n), dim3(256), (size_t)0, (const float *)Y.DO, Y.maxDO, (const float *)(Y.PROJ + L.dC + 2 * L.s.heads), Y.maxP,
                                (const float *)L.onorm, L.s.heads, L.s.value_dim, Y.c.norm_eps, h16 ? (float *)nullptr : Y.ATT32, h16 ? Y.ATT16 : (ly::bf16 *)nullptr, L.gd))) return rc;
             nl += 3;
@@ -331,7 +343,8 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
             ra.heads = L.s.heads; ra.kv_heads = L.s.kv_heads; ra.dk = L.s.key_dim; ra.dv = L.s.value_dim; ra.rope_dims = L.s.rope_dims; ra.rope_layout = L.s.rope_layout;
             ra.cs = L.rope; ra.temp = L.temp; ra.talk = L.talk; ra.value_from_key = L.s.value_from_key; ra.ring = Y.ring;
             qsrc = Y.Q; ldq = L.s.heads * L.dk_eff;
-            rc = launch_k(p, false, ly::k_rope_mix_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, ra, (const float *)L.b_proj, Y.Q, ldq, R.kc, R.vc, R.kc16, R.vc16, st);
+            rc = launch_k(p, false, ly::k_rope_mix_prep, dim3(n, L.s.heads + 1), dim3(ROPE_MIX_THREADS), (size_t)(L.qd > L.kd ? L.qd : L.kd) * 4, (const float *)Y.PROJ, Y.maxP, ra,
+                          (const float *)L.b_proj, Y.Q, ldq, R.kc, R.vc, R.kc16, R.vc16, st);
         } else
             rc = launch_k(p, false, ly::k_qk_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, wa, (const float *)L.b_proj, R.kc, R.vc, R.kc16, R.vc16, st);
         if (rc) return rc;
@@ -522,8 +535,8 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             L.dC = 2 * L.qd + L.vd;
             L.Pn = L.dC + 2 * s.heads + L.gr;
             L.P = pad ? (L.Pn + 127) / 128 * 128 : L.Pn;
-            if (ly::delta_rule_smem_floats(s.key_dim) * 4 > (size_t)Y.smem_max || (size_t)L.dC * 4 > (size_t)Y.smem_max)
-                return fail(p, B200_ERR_UNSUPPORTED, "layer %d: a state tile of key size %d or %d convolved channels exceed the shared memory of a CTA", l, s.key_dim, L.dC);
+            if ((!ly::delta_reg_rows(s.key_dim) && ly::delta_rule_smem_floats(s.key_dim) * 4 > (size_t)Y.smem_max) || (size_t)(s.key_dim > s.value_dim ? s.key_dim : s.value_dim) * 4 > (size_t)Y.smem_max)
+                return fail(p, B200_ERR_UNSUPPORTED, "layer %d: a state tile of key size %d or a head of %d values exceeds the shared memory of a CTA", l, s.key_dim, s.value_dim);
             if (L.P > Y.maxP) Y.maxP = L.P;
             if (L.gd > Y.maxO) Y.maxO = L.gd;
             if (L.dC + 2 * s.heads > Y.maxD) Y.maxD = L.dC + 2 * s.heads;
@@ -577,6 +590,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             CK(set_max_dyn(ly::k_window_attention_mma<128, 64>, Y.smem_max));
             CK(set_max_dyn(ly::k_window_attention_mma<256, 128>, Y.smem_max));
             CK(set_max_dyn(ly::k_delta_prep, Y.smem_max));
+            CK(set_max_dyn(ly::k_rope_mix_prep, Y.smem_max));
             CK(set_max_dyn(ly::k_delta_rule, Y.smem_max));
             attrs = true;
         }
@@ -741,7 +755,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         }
         if (L.s.mixer == B200_MIXER_GATED_DELTA) {
             // the run's recurrent state and its ring of convolution inputs (position j in slot j % cring)
-            const size_t sb = (size_t)L.s.heads * L.s.key_dim * L.s.value_dim * 4, cb = (size_t)Y.cring * L.dC * 4;
+            const size_t sb = ly::delta_state_floats(L.s.heads, L.s.key_dim, L.s.value_dim) * 4, cb = (size_t)Y.cring * L.dC * 4;
             if ((rc = dalloc(p, &R.S, sb))) return rc;
             if ((rc = dalloc(p, &R.cstate, cb))) return rc;
             CK(cudaMemset(R.S, 0, sb));
@@ -922,7 +936,7 @@ static int ly_kv_reset(b200_plan *p) {
     for (LyRun &R : Y.runs) {
         if (R.S) {
             const LyLayer &L = Y.layers[R.layer];
-            CK(cudaMemsetAsync(R.S, 0, (size_t)L.s.heads * L.s.key_dim * L.s.value_dim * 4, p->stream));
+            CK(cudaMemsetAsync(R.S, 0, ly::delta_state_floats(L.s.heads, L.s.key_dim, L.s.value_dim) * 4, p->stream));
             CK(cudaMemsetAsync(R.cstate, 0, (size_t)Y.cring * L.dC * 4, p->stream));
         }
         if (!R.own || !R.kc) continue;
@@ -951,7 +965,7 @@ static int ly_read_buffer(b200_plan *p, const char *name, int layer, void *dst, 
         if (layer < 0 || layer >= (int)Y.runs.size() || !Y.runs[layer].S) return fail(p, B200_ERR_BAD_ARG, "run %d has no %s", layer, name);
         const LyLayer &L = Y.layers[Y.runs[layer].layer];
         src = s == "delta_state" ? Y.runs[layer].S : Y.runs[layer].cstate;
-        sz = s == "delta_state" ? (size_t)L.s.heads * L.s.key_dim * L.s.value_dim * 4 : (size_t)Y.cring * L.dC * 4;
+        sz = s == "delta_state" ? ly::delta_state_floats(L.s.heads, L.s.key_dim, L.s.value_dim) * 4 : (size_t)Y.cring * L.dC * 4;
     } else return fail(p, B200_ERR_BAD_ARG, "unknown buffer %s", name);
     if (bytes < sz) sz = bytes;
     CK(cudaSetDevice(p->device));

@@ -296,7 +296,7 @@ int b200_kv_reset(b200_plan *plan);
 
 /* Test/diagnostic read-back of a named device buffer into host memory.  Names:
  * "x","xb","q","k","v","hb","logits","key_cache","value_cache","xq","xs"; layered plans with a gated-delta run: "delta_state"
- * ([heads][key_dim][value_dim]) and "conv_state" (the ring of convolution inputs).  `layer` selects the
+ * (the recurrent state of the run, in the recurrence kernel's own order) and "conv_state" (the ring of convolution inputs).  `layer` selects the
  * layer for the KV caches (ignored otherwise).  Copies min(bytes, buffer size).  Layered plans: `layer` is the layer RUN;
  * a latent-attention run has ONE cache, "key_cache" = rows [latent | rotated shared key part], and no "value_cache". */
 int b200_read_buffer(b200_plan *plan, const char *name, int32_t layer, void *dst, size_t bytes);
