@@ -205,13 +205,16 @@ __global__ void __launch_bounds__(DELTA_COLS) k_delta_rule(const float *__restri
 }
 
 // The same recurrence with the state in REGISTERS (key sizes up to 8 * R, R = 1, 2, 4, 8 or 16): grid (heads, column tiles of DR_COLS),
-// 256 threads.  A column of S is shared by DR_SLICES = 8 neighbouring lanes, lane s holding rows s, s + 8, s + 16, ...; the two
-// products S^T k and S^T q are R multiply-adds per lane and a three-step shuffle.  Columns are independent, a warp owns four of them
-// completely, so the only block-wide step is staging DR_TB tokens of k, q, v, beta and decay in shared memory at a time (and
-// writing their read-outs back coalesced).  The state buffer is private to this kernel: [head][tile][R][thread].
-#define DR_COLS 32
+// DR_THREADS threads.  A column of S is shared by DR_SLICES = 8 neighbouring lanes, lane s holding rows s * R .. s * R + R - 1; the two
+// products S^T k and S^T q are R multiply-adds per lane (four partial sums) and a three-step shuffle.  Columns are independent and a
+// warp owns four of them completely, so the only block-wide step is staging DR_TB tokens of k, q, v, beta and decay in shared memory
+// at a time (cp.async, double buffered: the next block lands while this one is computed; slices padded by four floats: the 128-bit
+// reads of the eight slices fall on distinct banks) and writing their read-outs back coalesced.  Within a token the chain
+// S^T k -> shuffles -> u -> S is what the next token waits for; the read-out's shuffles ride one token behind, interleaved with it.  Few columns per CTA on purpose: the recurrence is a chain of dependent steps per token, so it wants many SMs with
+// one warp per scheduler rather than few SMs with many.  The state buffer is private to this kernel: [head][tile][R][thread].
+#define DR_COLS 16
 #define DR_SLICES 8
-#define DR_THREADS 256
+#define DR_THREADS (DR_COLS * DR_SLICES)
 #define DR_TB 16
 __host__ __device__ inline int delta_reg_rows(int dk) { return dk <= 8 ? 1 : dk <= 16 ? 2 : dk <= 32 ? 4 : dk <= 64 ? 8 : dk <= 128 ? 16 : 0; } // 0: the shared-memory kernel
 __host__ __device__ inline size_t delta_state_floats(int heads, int dk, int dv) {
@@ -219,60 +222,103 @@ __host__ __device__ inline size_t delta_state_floats(int heads, int dk, int dv) 
     return R ? (size_t)heads * ((dv + DR_COLS - 1) / DR_COLS) * R * DR_THREADS : (size_t)heads * dk * dv;
 }
 
+__device__ __forceinline__ void cp_async4(void *dst, const void *src, bool valid) { // 4 bytes, zero-filled when !valid
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int nbytes = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(nbytes) : "memory");
+}
+
 template <int R>
 __global__ void __launch_bounds__(DR_THREADS) k_delta_rule_reg(const float *__restrict__ D, int ldd, DeltaArgs a, float *__restrict__ S, int n, float *__restrict__ O, int ldo,
                                                                const StepState *__restrict__ st) {
-    constexpr int KR = DR_SLICES * R; // key rows the threads cover (>= dk; the rest multiply zeros)
-    __shared__ float ks[DR_TB][KR], qs[DR_TB][KR], vs[DR_TB][DR_COLS], os[DR_TB][DR_COLS], bd[DR_TB][2];
+    constexpr int RP = R >= 4 ? R + 4 : R, KR = DR_SLICES * RP; // floats per slice / per token in shared memory
+    __shared__ __align__(16) float ks[2][DR_TB][KR], qs[2][DR_TB][KR];
+    __shared__ float vs[2][DR_TB][DR_COLS], bd[2][DR_TB][2], os[DR_TB][DR_COLS];
     const int h = blockIdx.x, tile = blockIdx.y, j0 = tile * DR_COLS, tid = threadIdx.x, lane = tid & 31;
     const int c = (tid >> 5) * 4 + (lane >> 3), s = lane & 7;
     const int dk = a.dk, dv = a.dv, g = h / (a.heads / a.kv_heads), C = delta_channels(a);
     float *Sg = S + ((size_t)h * gridDim.y + tile) * R * DR_THREADS + tid;
     float Sr[R];
     const bool fresh = st->pos == 0;
-#pragma unroll
-    for (int i = 0; i < R; i++) Sr[i] = fresh ? 0.0f : Sg[(size_t)i * DR_THREADS];
-    for (int t0 = 0; t0 < n; t0 += DR_TB) {
+    // the tokens of block t0 travel global -> shared asynchronously while the previous block is computed
+    auto stage = [&](int buf, int t0) {
         const int nb = n - t0 < DR_TB ? n - t0 : DR_TB;
-        for (int e = tid; e < nb * KR; e += DR_THREADS) {
-            const int t = e / KR, i = e % KR;
+        for (int e = tid; e < nb * DR_SLICES * R; e += DR_THREADS) {
+            const int t = e / (DR_SLICES * R), i = e % (DR_SLICES * R); // key row i belongs to slice i / R
             const float *d = D + (size_t)(t0 + t) * ldd;
-            ks[t][i] = i < dk ? d[(size_t)(a.kv_heads + g) * dk + i] : 0.0f;
-            qs[t][i] = i < dk ? d[(size_t)g * dk + i] : 0.0f;
+            const int at = (i / R) * RP + i % R;
+            const bool ok = i < dk;
+            cp_async4(&ks[buf][t][at], ok ? d + (size_t)(a.kv_heads + g) * dk + i : D, ok);
+            cp_async4(&qs[buf][t][at], ok ? d + (size_t)g * dk + i : D, ok);
         }
         for (int e = tid; e < nb * DR_COLS; e += DR_THREADS) {
             const int t = e / DR_COLS, cc = e % DR_COLS;
-            vs[t][cc] = j0 + cc < dv ? D[(size_t)(t0 + t) * ldd + 2 * a.kv_heads * dk + (size_t)h * dv + j0 + cc] : 0.0f;
+            const bool ok = j0 + cc < dv;
+            cp_async4(&vs[buf][t][cc], ok ? D + (size_t)(t0 + t) * ldd + 2 * a.kv_heads * dk + (size_t)h * dv + j0 + cc : D, ok);
         }
-        if (tid < nb * 2) bd[tid >> 1][tid & 1] = D[(size_t)(t0 + (tid >> 1)) * ldd + C + (tid & 1) * a.heads + h];
-        __syncthreads();
-        for (int t = 0; t < nb; t++) {
-            const float beta = bd[t][0], decay = bd[t][1];
-            float kr[R];
-            float rd = 0.0f;
+        if (tid < nb * 2) cp_async4(&bd[buf][tid >> 1][tid & 1], D + (size_t)(t0 + (tid >> 1)) * ldd + C + (tid & 1) * a.heads + h, true);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, 0);
 #pragma unroll
-            for (int i = 0; i < R; i++) { kr[i] = ks[t][i * DR_SLICES + s]; rd = fmaf(Sr[i], kr[i], rd); }
-            rd += __shfl_xor_sync(0xffffffffu, rd, 1);
-            rd += __shfl_xor_sync(0xffffffffu, rd, 2);
-            rd += __shfl_xor_sync(0xffffffffu, rd, 4);
-            const float u = beta * (vs[t][c] - decay * rd);
-            float o = 0.0f;
+    for (int i = 0; i < R; i++) Sr[i] = fresh ? 0.0f : Sg[(size_t)i * DR_THREADS];
+    int buf = 0;
+    for (int t0 = 0; t0 < n; t0 += DR_TB, buf ^= 1) {
+        const int nb = n - t0 < DR_TB ? n - t0 : DR_TB;
+        if (t0 + DR_TB < n) {
+            stage(buf ^ 1, t0 + DR_TB); // that buffer was last read before the barrier that ended the previous iteration
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        auto load = [&](int t, float (&kr)[R], float (&qr)[R]) {
+            if (R >= 4) {
+#pragma unroll
+                for (int i = 0; i < R; i += 4) {
+                    *reinterpret_cast<float4 *>(&kr[i]) = *reinterpret_cast<const float4 *>(&ks[buf][t][s * RP + i]);
+                    *reinterpret_cast<float4 *>(&qr[i]) = *reinterpret_cast<const float4 *>(&qs[buf][t][s * RP + i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < R; i++) { kr[i] = ks[buf][t][s * RP + i]; qr[i] = qs[buf][t][s * RP + i]; }
+            }
+        };
+        float kr[R], qr[R], kn[R], qn[R];
+        load(0, kr, qr);
+        float op = 0.0f; // read-out of the previous token, summed over the slices one shuffle step behind the current token's S^T k
+        for (int t = 0; t < nb; t++) {
+            const float beta = bd[buf][t][0], decay = bd[buf][t][1], v = vs[buf][t][c];
+            float r4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int i = 0; i < R; i++) r4[i & 3] = fmaf(Sr[i], kr[i], r4[i & 3]);
+            if (t + 1 < nb) load(t + 1, kn, qn); // in flight during the shuffles below
+            float rd = (r4[0] + r4[1]) + (r4[2] + r4[3]);
+#pragma unroll
+            for (int m = 1; m < DR_SLICES; m <<= 1) {
+                const float x = __shfl_xor_sync(0xffffffffu, rd, m), y = __shfl_xor_sync(0xffffffffu, op, m);
+                rd += x;
+                op += y;
+            }
+            if (s == 0 && t > 0) os[t - 1][c] = op;
+            const float u = beta * (v - decay * rd);
+            float o4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int i = 0; i < R; i++) {
                 Sr[i] = fmaf(kr[i], u, decay * Sr[i]);
-                o = fmaf(Sr[i], qs[t][i * DR_SLICES + s], o);
+                o4[i & 3] = fmaf(Sr[i], qr[i], o4[i & 3]);
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
-            if (s == 0) os[t][c] = o;
+            op = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+#pragma unroll
+            for (int i = 0; i < R; i++) { kr[i] = kn[i]; qr[i] = qn[i]; }
         }
+#pragma unroll
+        for (int m = 1; m < DR_SLICES; m <<= 1) op += __shfl_xor_sync(0xffffffffu, op, m);
+        if (s == 0) os[nb - 1][c] = op;
         __syncthreads();
         for (int e = tid; e < nb * DR_COLS; e += DR_THREADS) {
             const int t = e / DR_COLS, cc = e % DR_COLS;
             if (j0 + cc < dv) O[(size_t)(t0 + t) * ldo + (size_t)h * dv + j0 + cc] = os[t][cc];
         }
-        // the next block's staging writes ks / qs / vs / bd only; os is rewritten after the barrier that follows the staging
+        // os is rewritten only after the barrier that follows the next block's wait
     }
 #pragma unroll
     for (int i = 0; i < R; i++) Sg[(size_t)i * DR_THREADS] = Sr[i];
