@@ -282,10 +282,10 @@ __global__ void __launch_bounds__(DR_THREADS) k_delta_rule_reg(const float *__re
                 for (int i = 0; i < R; i++) { kr[i] = ks[buf][t][s * RP + i]; qr[i] = qs[buf][t][s * RP + i]; }
             }
         };
-        float kr[R], qr[R], kn[R], qn[R];
-        load(0, kr, qr);
+        float ka[R], qa[R], kb[R], qb[R]; // two register sets: the next token's k and q load while the current one's shuffles run
+        load(0, ka, qa);
         float op = 0.0f; // read-out of the previous token, summed over the slices one shuffle step behind the current token's S^T k
-        for (int t = 0; t < nb; t++) {
+        auto token = [&](int t, const float (&kr)[R], const float (&qr)[R], float (&kn)[R], float (&qn)[R]) {
             const float beta = bd[buf][t][0], decay = bd[buf][t][1], v = vs[buf][t][c];
             float r4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -307,8 +307,10 @@ __global__ void __launch_bounds__(DR_THREADS) k_delta_rule_reg(const float *__re
                 o4[i & 3] = fmaf(Sr[i], qr[i], o4[i & 3]);
             }
             op = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-#pragma unroll
-            for (int i = 0; i < R; i++) { kr[i] = kn[i]; qr[i] = qn[i]; }
+        };
+        for (int t = 0; t < nb; t += 2) {
+            token(t, ka, qa, kb, qb);
+            if (t + 1 < nb) token(t + 1, kb, qb, ka, qa);
         }
 #pragma unroll
         for (int m = 1; m < DR_SLICES; m <<= 1) op += __shfl_xor_sync(0xffffffffu, op, m);
