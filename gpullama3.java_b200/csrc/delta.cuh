@@ -31,11 +31,13 @@ struct RopeMixArgs {
     int ring;                    // position j lives in slot j % ring
 };
 
-// grid (rows, heads + 1), 128 threads; dynamic shared memory: heads * dk floats.  P row: [q: heads*dk | k: kv_heads*dk | v: kv_heads*dv
-// (absent with value_from_key) | ...].  CTA (r, h < heads) biases and rotates ALL query heads of the row into shared memory (every
-// mixed query needs them all; the row in P stays as projected) and writes head h's query: heads * (talk ? kv_heads * dk : dk) entries
-// per Q row (ldq).  CTA (r, heads) owns the key side: bias, value row = unrotated key (or the value projection), rotation, key row.
+// grid (rows, ceil(heads / ROPE_MIX_HEADS) + 1), 128 threads; dynamic shared memory: max(heads, kv_heads) * dk floats.  P row:
+// [q: heads*dk | k: kv_heads*dk | v: kv_heads*dv (absent with value_from_key) | ...].  A query-side CTA biases and rotates ALL query heads
+// of the row into shared memory (every mixed query needs them all; the row in P stays as projected) and writes the queries of its
+// ROPE_MIX_HEADS heads: heads * (talk ? kv_heads * dk : dk) entries per Q row (ldq).  The last CTA of a row owns the key side: bias,
+// value row = unrotated key (or the value projection), rotation, key row.
 #define ROPE_MIX_THREADS 128
+#define ROPE_MIX_HEADS 4
 __global__ void __launch_bounds__(ROPE_MIX_THREADS) k_rope_mix_prep(const float *__restrict__ P, int ldp, RopeMixArgs a, const float *__restrict__ bias, float *__restrict__ Q, int ldq,
                                                                     float *__restrict__ kc, float *__restrict__ vc, bf16 *__restrict__ kc16, bf16 *__restrict__ vc16,
                                                                     const StepState *__restrict__ st) {
@@ -45,7 +47,7 @@ __global__ void __launch_bounds__(ROPE_MIX_THREADS) k_rope_mix_prep(const float 
     const float *p = P + (size_t)r * ldp;
     const int pos = st->pos + r, slot = pos % a.ring, half = a.rope_dims / 2;
     const float *cs = a.cs + (size_t)pos * half * 2;
-    const bool key_side = (int)blockIdx.y == a.heads;
+    const bool key_side = blockIdx.y == gridDim.y - 1;
     // this CTA's vectors, biased: all query heads, or all key heads
     const int off = key_side ? qd : 0, len = key_side ? kd : qd, nh = key_side ? a.kv_heads : a.heads;
     for (int i = tid; i < len; i += ROPE_MIX_THREADS) xs[i] = p[off + i] + (bias ? bias[off + i] : 0.0f);
@@ -76,19 +78,19 @@ __global__ void __launch_bounds__(ROPE_MIX_THREADS) k_rope_mix_prep(const float 
         }
         return;
     }
-    const int h = blockIdx.y;
+    const int h0 = blockIdx.y * ROPE_MIX_HEADS, h1 = h0 + ROPE_MIX_HEADS < a.heads ? h0 + ROPE_MIX_HEADS : a.heads;
     if (a.talk) {
         const int group = a.heads / a.kv_heads;
-        float *qo = Q + (size_t)r * ldq + (size_t)h * kd;
-        for (int c = tid; c < kd; c += ROPE_MIX_THREADS) {
-            const int kv = c / a.dk, d = c % a.dk;
+        float *qo = Q + (size_t)r * ldq + (size_t)h0 * kd;
+        for (int e = tid; e < (h1 - h0) * kd; e += ROPE_MIX_THREADS) {
+            const int h = h0 + e / kd, c = e % kd, kv = c / a.dk, d = c % a.dk;
             float s = 0.0f;
             for (int m = kv * group; m < (kv + 1) * group; m++) s = fmaf(a.talk[h * a.heads + m] * (a.temp ? a.temp[m] : 1.0f), xs[(size_t)m * a.dk + d], s);
-            qo[c] = s;
+            qo[e] = s;
         }
     } else {
-        float *qo = Q + (size_t)r * ldq + (size_t)h * a.dk;
-        for (int d = tid; d < a.dk; d += ROPE_MIX_THREADS) qo[d] = a.temp ? xs[(size_t)h * a.dk + d] * a.temp[h] : xs[(size_t)h * a.dk + d];
+        float *qo = Q + (size_t)r * ldq;
+        for (int e = h0 * a.dk + tid; e < h1 * a.dk; e += ROPE_MIX_THREADS) qo[e] = a.temp ? xs[e] * a.temp[e / a.dk] : xs[e];
     }
 }
 
@@ -204,19 +206,20 @@ __global__ void __launch_bounds__(DELTA_COLS) k_delta_rule(const float *__restri
         for (int i = 0; i < dk; i++) Sg[(size_t)i * dv + j] = Ss[i * DELTA_COLS + tid];
 }
 
-// The same recurrence with the state in REGISTERS (key sizes up to 8 * R, R = 1, 2, 4, 8 or 16): grid (heads, column tiles of DR_COLS),
-// DR_THREADS threads.  A column of S is shared by DR_SLICES = 8 neighbouring lanes, lane s holding rows s * R .. s * R + R - 1; the two
-// products S^T k and S^T q are R multiply-adds per lane (four partial sums) and a three-step shuffle.  Columns are independent and a
-// warp owns four of them completely, so the only block-wide step is staging DR_TB tokens of k, q, v, beta and decay in shared memory
-// at a time (cp.async, double buffered: the next block lands while this one is computed; slices padded by four floats: the 128-bit
-// reads of the eight slices fall on distinct banks) and writing their read-outs back coalesced.  Within a token the chain
-// S^T k -> shuffles -> u -> S is what the next token waits for; the read-out's shuffles ride one token behind, interleaved with it.  Few columns per CTA on purpose: the recurrence is a chain of dependent steps per token, so it wants many SMs with
-// one warp per scheduler rather than few SMs with many.  The state buffer is private to this kernel: [head][tile][R][thread].
+// The same recurrence with the state in REGISTERS (key sizes up to 16 * R, R = 1, 2, 4 or 8): grid (heads, column tiles of DR_COLS),
+// DR_THREADS threads.  A column of S is shared by DR_SLICES = 16 neighbouring lanes, lane s holding rows s * R .. s * R + R - 1; the two
+// products S^T k and S^T q are R multiply-adds per lane (four partial sums) and a four-step shuffle.  Columns are independent and a
+// warp owns two of them completely, so the only block-wide step is staging DR_TB tokens of k, q, v, beta and decay in shared memory
+// at a time (cp.async, double buffered: the next block lands while this one is computed; slices of eight padded by four floats: the
+// 128-bit reads of a quarter warp fall on distinct banks) and writing their read-outs back coalesced.  Within a token the chain
+// S^T k -> shuffles -> u -> S is what the next token waits for; the read-out's shuffles ride one token behind, interleaved with it.
+// Sixteen lanes per column rather than eight: the per-token chain gets shorter and every scheduler has two warps to alternate
+// between.  The state buffer is private to this kernel: [head][tile][R][thread].
 #define DR_COLS 16
-#define DR_SLICES 8
+#define DR_SLICES 16
 #define DR_THREADS (DR_COLS * DR_SLICES)
-#define DR_TB 16
-__host__ __device__ inline int delta_reg_rows(int dk) { return dk <= 8 ? 1 : dk <= 16 ? 2 : dk <= 32 ? 4 : dk <= 64 ? 8 : dk <= 128 ? 16 : 0; } // 0: the shared-memory kernel
+#define DR_TB 8
+__host__ __device__ inline int delta_reg_rows(int dk) { return dk <= 16 ? 1 : dk <= 32 ? 2 : dk <= 64 ? 4 : dk <= 128 ? 8 : 0; } // 0: the shared-memory kernel
 __host__ __device__ inline size_t delta_state_floats(int heads, int dk, int dv) {
     const int R = delta_reg_rows(dk);
     return R ? (size_t)heads * ((dv + DR_COLS - 1) / DR_COLS) * R * DR_THREADS : (size_t)heads * dk * dv;
@@ -231,11 +234,11 @@ __device__ __forceinline__ void cp_async4(void *dst, const void *src, bool valid
 template <int R>
 __global__ void __launch_bounds__(DR_THREADS) k_delta_rule_reg(const float *__restrict__ D, int ldd, DeltaArgs a, float *__restrict__ S, int n, float *__restrict__ O, int ldo,
                                                                const StepState *__restrict__ st) {
-    constexpr int RP = R >= 4 ? R + 4 : R, KR = DR_SLICES * RP; // floats per slice / per token in shared memory
+    constexpr int RP = R > 4 ? R + 4 : R, KR = DR_SLICES * RP; // floats per slice / per token in shared memory
     __shared__ __align__(16) float ks[2][DR_TB][KR], qs[2][DR_TB][KR];
     __shared__ float vs[2][DR_TB][DR_COLS], bd[2][DR_TB][2], os[DR_TB][DR_COLS];
     const int h = blockIdx.x, tile = blockIdx.y, j0 = tile * DR_COLS, tid = threadIdx.x, lane = tid & 31;
-    const int c = (tid >> 5) * 4 + (lane >> 3), s = lane & 7;
+    const int c = (tid >> 5) * (32 / DR_SLICES) + lane / DR_SLICES, s = lane % DR_SLICES;
     const int dk = a.dk, dv = a.dv, g = h / (a.heads / a.kv_heads), C = delta_channels(a);
     float *Sg = S + ((size_t)h * gridDim.y + tile) * R * DR_THREADS + tid;
     float Sr[R];

@@ -325,7 +325,6 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
             case 2: rc = launch_k(p, false, ly::k_delta_rule_reg<2>, rgrid, rblock, (size_t)0, (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st); break;
             case 4: rc = launch_k(p, false, ly::k_delta_rule_reg<4>, rgrid, rblock, (size_t)0, (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st); break;
             case 8: rc = launch_k(p, false, ly::k_delta_rule_reg<8>, rgrid, rblock, (size_t)0, (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st); break;
-            case 16: rc = launch_k(p, false, ly::k_delta_rule_reg<16>, rgrid, rblock, (size_t)0, (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st); break;
             default: // key sizes above 128: the state tile in shared memory, one thread per column
                 rc = launch_k(p, false, ly::k_delta_rule, dim3(L.s.heads, (L.s.value_dim + DELTA_COLS - 1) / DELTA_COLS), dim3(DELTA_COLS), ly::delta_rule_smem_floats(L.s.key_dim) * 4,
                               (const float *)Y.DLT, Y.maxD, da, R.S, n, Y.DO, Y.maxDO, st);
@@ -343,7 +342,7 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
             ra.heads = L.s.heads; ra.kv_heads = L.s.kv_heads; ra.dk = L.s.key_dim; ra.dv = L.s.value_dim; ra.rope_dims = L.s.rope_dims; ra.rope_layout = L.s.rope_layout;
             ra.cs = L.rope; ra.temp = L.temp; ra.talk = L.talk; ra.value_from_key = L.s.value_from_key; ra.ring = Y.ring;
             qsrc = Y.Q; ldq = L.s.heads * L.dk_eff;
-            rc = launch_k(p, false, ly::k_rope_mix_prep, dim3(n, L.s.heads + 1), dim3(ROPE_MIX_THREADS), (size_t)(L.qd > L.kd ? L.qd : L.kd) * 4, (const float *)Y.PROJ, Y.maxP, ra,
+            rc = launch_k(p, false, ly::k_rope_mix_prep, dim3(n, (L.s.heads + ROPE_MIX_HEADS - 1) / ROPE_MIX_HEADS + 1), dim3(ROPE_MIX_THREADS), (size_t)(L.qd > L.kd ? L.qd : L.kd) * 4, (const float *)Y.PROJ, Y.maxP, ra,
                           (const float *)L.b_proj, Y.Q, ldq, R.kc, R.vc, R.kc16, R.vc16, st);
         } else
             rc = launch_k(p, false, ly::k_qk_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, wa, (const float *)L.b_proj, R.kc, R.vc, R.kc16, R.vc16, st);
