@@ -31,16 +31,16 @@ struct RopeMixArgs {
     int ring;                    // position j lives in slot j % ring
 };
 
-// grid (rows, ceil(heads / ROPE_MIX_HEADS) + 1), 128 threads; dynamic shared memory: max(heads, kv_heads) * dk floats.  P row:
+// grid (rows, ceil(heads / hpc) + 1), 128 threads (hpc = query heads per CTA: ROPE_MIX_HEADS for a chunk of rows, 1 for the decode step's single row); dynamic shared memory: max(heads, kv_heads) * dk floats.  P row:
 // [q: heads*dk | k: kv_heads*dk | v: kv_heads*dv (absent with value_from_key) | ...].  A query-side CTA biases and rotates ALL query heads
 // of the row into shared memory (every mixed query needs them all; the row in P stays as projected) and writes the queries of its
-// ROPE_MIX_HEADS heads: heads * (talk ? kv_heads * dk : dk) entries per Q row (ldq).  The last CTA of a row owns the key side: bias,
+// hpc heads: heads * (talk ? kv_heads * dk : dk) entries per Q row (ldq).  The last CTA of a row owns the key side: bias,
 // value row = unrotated key (or the value projection), rotation, key row.
 #define ROPE_MIX_THREADS 128
 #define ROPE_MIX_HEADS 4
 __global__ void __launch_bounds__(ROPE_MIX_THREADS) k_rope_mix_prep(const float *__restrict__ P, int ldp, RopeMixArgs a, const float *__restrict__ bias, float *__restrict__ Q, int ldq,
                                                                     float *__restrict__ kc, float *__restrict__ vc, bf16 *__restrict__ kc16, bf16 *__restrict__ vc16,
-                                                                    const StepState *__restrict__ st) {
+                                                                    const StepState *__restrict__ st, int hpc) {
     extern __shared__ __align__(16) float xs[];
     const int r = blockIdx.x, tid = threadIdx.x;
     const int qd = a.heads * a.dk, kd = a.kv_heads * a.dk, vd = a.kv_heads * a.dv;
@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(ROPE_MIX_THREADS) k_rope_mix_prep(const float 
         }
         return;
     }
-    const int h0 = blockIdx.y * ROPE_MIX_HEADS, h1 = h0 + ROPE_MIX_HEADS < a.heads ? h0 + ROPE_MIX_HEADS : a.heads;
+    const int h0 = blockIdx.y * hpc, h1 = h0 + hpc < a.heads ? h0 + hpc : a.heads;
     if (a.talk) {
         const int group = a.heads / a.kv_heads;
         float *qo = Q + (size_t)r * ldq + (size_t)h0 * kd;

@@ -342,8 +342,9 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
             ra.heads = L.s.heads; ra.kv_heads = L.s.kv_heads; ra.dk = L.s.key_dim; ra.dv = L.s.value_dim; ra.rope_dims = L.s.rope_dims; ra.rope_layout = L.s.rope_layout;
             ra.cs = L.rope; ra.temp = L.temp; ra.talk = L.talk; ra.value_from_key = L.s.value_from_key; ra.ring = Y.ring;
             qsrc = Y.Q; ldq = L.s.heads * L.dk_eff;
-            rc = launch_k(p, false, ly::k_rope_mix_prep, dim3(n, (L.s.heads + ROPE_MIX_HEADS - 1) / ROPE_MIX_HEADS + 1), dim3(ROPE_MIX_THREADS), (size_t)(L.qd > L.kd ? L.qd : L.kd) * 4, (const float *)Y.PROJ, Y.maxP, ra,
-                          (const float *)L.b_proj, Y.Q, ldq, R.kc, R.vc, R.kc16, R.vc16, st);
+            const int hpc = decode ? 1 : ROPE_MIX_HEADS; // one row: a CTA per head; a chunk: several heads share the rotation of the row
+            rc = launch_k(p, false, ly::k_rope_mix_prep, dim3(n, (L.s.heads + hpc - 1) / hpc + 1), dim3(ROPE_MIX_THREADS), (size_t)(L.qd > L.kd ? L.qd : L.kd) * 4, (const float *)Y.PROJ, Y.maxP, ra,
+                          (const float *)L.b_proj, Y.Q, ldq, R.kc, R.vc, R.kc16, R.vc16, st, hpc);
         } else
             rc = launch_k(p, false, ly::k_qk_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, wa, (const float *)L.b_proj, R.kc, R.vc, R.kc16, R.vc16, st);
         if (rc) return rc;
