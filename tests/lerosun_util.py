@@ -35,6 +35,8 @@ def configs(S):
         "window_one": S.lerosun_config(32, 40, [A(2, 1, 16, 1, 48), D(1, 1, 4, 4, 2, 16), A(2, 2, 16, 200, 48)]),
         "delta_only": S.lerosun_config(56, 70, [D(4, 4, 9, 11, 3, 60), D(2, 1, 32, 130, 4, None)]),
         "attention_only": S.lerosun_config(56, 70, [A(4, 1, 14, 8, 60, rot_dims=6), A(8, 8, 4, 13, None, rot_dims=4, base=7.0)]),
+        # key sizes beyond what the delta rule keeps in registers (the shared-memory kernel) and a wide folded key row
+        "big_key": S.lerosun_config(44, 50, [D(2, 1, 136, 20, 2, None), A(4, 4, 36, 10, 32, rot_dims=18), D(3, 3, 130, 70, 3, 24)]),
         # shapes the tensor-core prefill takes: widths in whole GEMM tiles; folded key rows / value sizes of 128 / 64, 64 / 64, 128 / 128, 256 / 128
         "tiles_a": S.lerosun_config(128, 256, [A(2, 2, 64, 70, 256), D(2, 1, 64, 64, 4, 128), A(4, 1, 64, 9, 256, rot_dims=64)], loop=(0, 2, 2)),
         "tiles_b": S.lerosun_config(256, 384, [D(2, 2, 128, 128, 3, None), A(2, 1, 128, 33, 128, rot_dims=32), A(4, 2, 128, 129, 384)]),

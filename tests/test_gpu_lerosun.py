@@ -66,7 +66,7 @@ def portions(plan, toks, sizes, batch):
 
 
 @pytest.mark.parametrize("compute", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["pair", "loop_mid", "loop_start_odd", "loop_once_end", "window_one", "delta_only", "attention_only", "tiles_a", "tiles_b"])
+@pytest.mark.parametrize("name", ["pair", "loop_mid", "loop_start_odd", "loop_once_end", "window_one", "delta_only", "attention_only", "big_key", "tiles_a", "tiles_b"])
 def test_every_layer_run_matches_oracle(pkg, name, compute):
     """Residual stream after every layer run and the logits: each mixer alone (delta_only, attention_only) and in every order."""
     S, O = pkg.synth, oracle()
@@ -85,7 +85,7 @@ def test_every_layer_run_matches_oracle(pkg, name, compute):
         plan.free()
 
 
-@pytest.mark.parametrize("name", ["loop_mid", "loop_start_odd", "delta_only", "tiles_a"])
+@pytest.mark.parametrize("name", ["loop_mid", "loop_start_odd", "delta_only", "big_key", "tiles_a"])
 def test_prefill_equals_token_by_token_decode(pkg, name):
     S, O = pkg.synth, oracle()
     cfg = configs(S)[name]
@@ -104,7 +104,7 @@ def test_prefill_equals_token_by_token_decode(pkg, name):
 
 
 @pytest.mark.parametrize("compute", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["loop_mid", "loop_start_odd"])
+@pytest.mark.parametrize("name", ["loop_mid", "loop_start_odd", "big_key"])
 def test_portions_of_every_size(pkg, name, compute):
     """The same prompt cut into portions of 2 .. 13 tokens (edges inside windows and inside the convolution's taps), then decoded one
     by one; the chunk capacity (7) is below the portion sizes, so portions are cut again, and both rings wrap."""
