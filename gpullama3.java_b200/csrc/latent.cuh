@@ -173,19 +173,71 @@ __global__ void __launch_bounds__(256) k_latent_prep(float *__restrict__ P, int 
 // ---------------------------------------------------------------------------------------------------------------------
 // Mixture of experts: router and grouping.
 // ---------------------------------------------------------------------------------------------------------------------
-// Router: logits z_e = <Wr[e], x> accumulated in FP32 (x FP32 or its BF16 rounding, Wr BF16), scores s_e = sigmoid(z_e), then the
-// `top` largest (the lowest index wins a tie); ids / wts [n][top] in order of falling score.  Four warps per CTA: with
-// rows_per_cta == 4 every warp owns a row, with rows_per_cta == 1 the four warps share the experts of one row (what the plan
-// launches: four times the warps in flight, and the kernel is bound by the latency of its loads; the router matrix is small
-// and stays in L2).  Dynamic shared memory: rows_per_cta * (E + experts) floats.
+// How the router's logits become expert ids and weights.  softmax == 0: scores sigmoid(z), the `top` largest, weight = score.
+// softmax == 1: scores s = softmax(z) over all router outputs, the `top` largest of s + correction are chosen, weight =
+// s / (sum of the chosen s + 1e-20) * scale.  Router outputs n_real .. are identity experts: they all get the id n_real.
+struct RouteMode {
+    int softmax;
+    const float *correction; // [experts] (softmax mode)
+    int n_real;              // experts with weights (<= experts)
+    float scale;
+};
+
+// One warp: z [experts] logits in shared memory (overwritten), sbuf [experts] scratch; ids / wts [top] in order of falling choice
+// score (the lowest index wins a tie).
+__device__ __forceinline__ void route_select(float *z, float *sbuf, int experts, int top, const RouteMode &m, int *ids, float *wts, int lane) {
+    if (m.softmax) {
+        float mx = -INFINITY;
+        for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.0f;
+        for (int e = lane; e < experts; e += 32) { const float w = expf(z[e] - mx); sbuf[e] = w; sum += w; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < experts; e += 32) { const float sc = sbuf[e] / sum; sbuf[e] = sc; z[e] = sc + m.correction[e]; }
+        __syncwarp();
+    }
+    float tot = 0.0f;
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int bi = experts;
+        for (int e = lane; e < experts; e += 32)
+            if (z[e] > best) { best = z[e]; bi = e; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (lane == 0) {
+            const int id = bi < experts ? bi : 0;
+            ids[k] = id < m.n_real ? id : m.n_real;
+            const float w = m.softmax ? (bi < experts ? sbuf[bi] : 0.0f) : 1.0f / (1.0f + expf(-best));
+            wts[k] = w;
+            tot += w;
+            if (bi < experts) z[bi] = -INFINITY; // taken
+        }
+        __syncwarp();
+    }
+    if (m.softmax && lane == 0)
+        for (int k = 0; k < top; k++) wts[k] = wts[k] / (tot + 1e-20f) * m.scale;
+}
+
+// Router: logits z_e = <Wr[e], x> accumulated in FP32 (x FP32 or its BF16 rounding, Wr BF16), then route_select; ids / wts
+// [n][top].  Wr may carry `extra` further rows behind the experts' whose logits go to extra_out [n][extra] (a gate computed
+// from the same input).  Four warps per CTA: with rows_per_cta == 4 every warp owns a row, with rows_per_cta == 1 the four
+// warps share the rows of one token (what the plan launches: four times the warps in flight, and the kernel is bound by the
+// latency of its loads; the router matrix is small and stays in L2).
+// Dynamic shared memory: rows_per_cta * (E + 2 * (experts + extra)) floats.
 template <typename IN_T>
 __global__ void __launch_bounds__(128) k_moe_route(const IN_T *__restrict__ X, const bf16 *__restrict__ Wr, int n, int E, int experts, int top, int rows_per_cta,
-                                                   int *__restrict__ ids, float *__restrict__ wts) {
+                                                   int *__restrict__ ids, float *__restrict__ wts, RouteMode m, int extra, float *__restrict__ extra_out) {
     extern __shared__ __align__(16) float sm[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool shared_row = rows_per_cta == 1;
     const int r = shared_row ? blockIdx.x : blockIdx.x * 4 + warp;
-    float *xs = sm + (shared_row ? 0 : (size_t)warp * E), *z = sm + (size_t)rows_per_cta * E + (shared_row ? 0 : (size_t)warp * experts);
+    const int zw = 2 * (experts + extra);
+    float *xs = sm + (shared_row ? 0 : (size_t)warp * E), *z = sm + (size_t)rows_per_cta * E + (shared_row ? 0 : (size_t)warp * zw);
     if (r < n) {
         if (shared_row) for (int i = tid; i < E; i += 128) xs[i] = (float)X[(size_t)r * E + i];
         else for (int i = lane; i < E; i += 32) xs[i] = (float)X[(size_t)r * E + i];
@@ -193,65 +245,33 @@ __global__ void __launch_bounds__(128) k_moe_route(const IN_T *__restrict__ X, c
     if (shared_row) __syncthreads(); else __syncwarp();
     if (r < n) {
         const bool vec = (E & 7) == 0 && (((size_t)Wr) & 15) == 0;
-        for (int e = shared_row ? warp : 0; e < experts; e += shared_row ? 4 : 1) {
+        for (int e = shared_row ? warp : 0; e < experts + extra; e += shared_row ? 4 : 1) {
             const float acc = dot_row_bf16(Wr + (size_t)e * E, xs, E, lane, vec); // 128-bit weight loads, FP32 accumulation
             if (lane == 0) z[e] = acc;
         }
     }
     if (shared_row) __syncthreads(); else __syncwarp();
     if (r >= n || (shared_row && warp != 0)) return;
-    for (int k = 0; k < top; k++) {
-        float best = -INFINITY;
-        int bi = experts;
-        for (int e = lane; e < experts; e += 32)
-            if (z[e] > best) { best = z[e]; bi = e; }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-        }
-        if (lane == 0) {
-            ids[(size_t)r * top + k] = bi < experts ? bi : 0;
-            wts[(size_t)r * top + k] = 1.0f / (1.0f + expf(-best));
-            if (bi < experts) z[bi] = -INFINITY; // taken
-        }
-        __syncwarp();
-    }
+    for (int e = lane; e < extra; e += 32) extra_out[(size_t)r * extra + e] = z[experts + e];
+    route_select(z, z + experts + extra, experts, top, m, ids + (size_t)r * top, wts + (size_t)r * top, lane);
 }
 
 // The decode step spreads the router's rows over several CTAs (k_matvec_bf16) and selects here: one warp, logits z [experts]
-// in, the `top` largest sigmoid scores out.  Dynamic shared memory: experts floats.
-__global__ void __launch_bounds__(32) k_moe_topk(const float *__restrict__ Z, int experts, int top, int *__restrict__ ids, float *__restrict__ wts) {
+// in, route_select out.  Dynamic shared memory: 2 * experts floats.
+__global__ void __launch_bounds__(32) k_moe_topk(const float *__restrict__ Z, int experts, int top, int *__restrict__ ids, float *__restrict__ wts, RouteMode m) {
     extern __shared__ __align__(16) float z[];
     const int lane = threadIdx.x;
     for (int e = lane; e < experts; e += 32) z[e] = Z[e];
     __syncwarp();
-    for (int k = 0; k < top; k++) {
-        float best = -INFINITY;
-        int bi = experts;
-        for (int e = lane; e < experts; e += 32)
-            if (z[e] > best) { best = z[e]; bi = e; }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-        }
-        if (lane == 0) {
-            ids[k] = bi < experts ? bi : 0;
-            wts[k] = 1.0f / (1.0f + expf(-best));
-            if (bi < experts) z[bi] = -INFINITY;
-        }
-        __syncwarp();
-    }
+    route_select(z, z + experts, experts, top, m, ids, wts, lane);
 }
 
 // One CTA: the slots 0 .. n_slots - 1 (slot = row * top + k, expert ids[slot]) sorted by expert into `perm`, and the list of
 // tiles (at most 64 slots of one expert each) the grouped projections run over; unused tiles get group -1.
 // Dynamic shared memory: 3 * experts ints.
+// Ids n_real .. experts - 1 are experts without weights (the identity): their slots are sorted like the others but their tiles get group -1.
 __global__ void __launch_bounds__(1024) k_moe_group(const int *__restrict__ ids, int n_slots, int experts, int max_tiles, int *__restrict__ perm,
-                                                    int *__restrict__ tile_group, int *__restrict__ tile_row0, int *__restrict__ tile_rows) {
+                                                    int *__restrict__ tile_group, int *__restrict__ tile_row0, int *__restrict__ tile_rows, int n_real) {
     extern __shared__ int smi[];
     int *count = smi, *offs = smi + experts, *cursor = smi + 2 * experts;
     const int tid = threadIdx.x;
@@ -264,7 +284,7 @@ __global__ void __launch_bounds__(1024) k_moe_group(const int *__restrict__ ids,
         for (int e = 0; e < experts; e++) {
             offs[e] = o;
             for (int b = 0; b < count[e] && t < max_tiles; b += 64, t++) {
-                tile_group[t] = e;
+                tile_group[t] = e < n_real ? e : -1;
                 tile_row0[t] = o + b;
                 tile_rows[t] = count[e] - b < 64 ? count[e] - b : 64;
             }
@@ -293,8 +313,11 @@ __global__ void __launch_bounds__(256) k_latent_spread(const bf16 *__restrict__ 
 // The same grouping for the tcgen05 projections: every expert's slots padded to whole 128-row tiles, so that a tile belongs to one
 // expert.  srt [max_tiles * 128]: slot of every padded row (-1: padding); slot_row [n_slots]: the inverse; row_scale: the slot's
 // routing weight (0 for padding); tile_group [max_tiles]: expert of every tile, -1 beyond the last.  Dynamic shared memory: 3 * experts ints.
+// Slots of ids >= n_real (experts without weights) get no row (slot_row -1); unit_scale: row_scale is 1 for every real row (the
+// routing weight is applied to the expert's output, elsewhere).
 __global__ void __launch_bounds__(1024) k_moe_group_padded(const int *__restrict__ ids, const float *__restrict__ wts, int n_slots, int experts, int max_tiles,
-                                                           int *__restrict__ srt, int *__restrict__ slot_row, float *__restrict__ row_scale, int *__restrict__ tile_group) {
+                                                           int *__restrict__ srt, int *__restrict__ slot_row, float *__restrict__ row_scale, int *__restrict__ tile_group,
+                                                           int n_real, int unit_scale) {
     extern __shared__ int smi[];
     int *count = smi, *offs = smi + experts, *cursor = smi + 2 * experts;
     const int tid = threadIdx.x;
@@ -305,7 +328,7 @@ __global__ void __launch_bounds__(1024) k_moe_group_padded(const int *__restrict
     __syncthreads();
     if (tid == 0) {
         int t = 0;
-        for (int e = 0; e < experts; e++) {
+        for (int e = 0; e < n_real; e++) {
             offs[e] = t * 128;
             for (int b = 0; b < count[e] && t < max_tiles; b += 128) tile_group[t++] = e;
         }
@@ -313,8 +336,10 @@ __global__ void __launch_bounds__(1024) k_moe_group_padded(const int *__restrict
     }
     __syncthreads();
     for (int s = tid; s < n_slots; s += 1024) {
-        const int e = ids[s], row = offs[e] + atomicAdd(&cursor[e], 1);
-        if (row < max_tiles * 128) { srt[row] = s; row_scale[row] = wts[s]; }
+        const int e = ids[s];
+        if (e >= n_real) { slot_row[s] = -1; continue; }
+        const int row = offs[e] + atomicAdd(&cursor[e], 1);
+        if (row < max_tiles * 128) { srt[row] = s; row_scale[row] = unit_scale ? 1.0f : wts[s]; }
         slot_row[s] = row;
     }
 }

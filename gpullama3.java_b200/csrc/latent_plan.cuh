@@ -292,13 +292,14 @@ static int ly_enqueue_parallel(b200_plan *p, bool decode, int n, const StepState
             const int F = s.ff_dim, X = s.ff_experts, top = s.ff_top;
             if (decode) { // one row: the router's rows stream through the multi-CTA matvec, one warp selects
                 if ((rc = ly_project<ly::EPI_STORE>(p, true, 1, Y.A2_32, nullptr, L.w_router, nullptr, X, E, Y.ZR, nullptr, X, 0))) return rc;
-                if ((rc = launch_k(p, false, ly::k_moe_topk, dim3(1), dim3(32), (size_t)X * 4, (const float *)Y.ZR, X, top, Y.moe_ids, Y.moe_wts))) return rc;
+                if ((rc = launch_k(p, false, ly::k_moe_topk, dim3(1), dim3(32), (size_t)2 * X * 4, (const float *)Y.ZR, X, top, Y.moe_ids, Y.moe_wts, ly::RouteMode{0, nullptr, X, 1.0f}))) return rc;
                 nl += 2;
             } else {
                 const int rpc = 1; // a CTA per row: four warps share the row's experts
-                const size_t rsm = (size_t)rpc * (E + X) * 4;
-                if (h16) rc = launch_k(p, false, ly::k_moe_route<ly::bf16>, dim3((n + rpc - 1) / rpc), dim3(128), rsm, (const ly::bf16 *)Y.A2_16, (const ly::bf16 *)L.w_router, n, E, X, top, rpc, Y.moe_ids, Y.moe_wts);
-                else rc = launch_k(p, false, ly::k_moe_route<float>, dim3((n + rpc - 1) / rpc), dim3(128), rsm, (const float *)Y.A2_32, (const ly::bf16 *)L.w_router, n, E, X, top, rpc, Y.moe_ids, Y.moe_wts);
+                const size_t rsm = (size_t)rpc * (E + 2 * X) * 4;
+                const ly::RouteMode rm{0, nullptr, X, 1.0f};
+                if (h16) rc = launch_k(p, false, ly::k_moe_route<ly::bf16>, dim3((n + rpc - 1) / rpc), dim3(128), rsm, (const ly::bf16 *)Y.A2_16, (const ly::bf16 *)L.w_router, n, E, X, top, rpc, Y.moe_ids, Y.moe_wts, rm, 0, (float *)nullptr);
+                else rc = launch_k(p, false, ly::k_moe_route<float>, dim3((n + rpc - 1) / rpc), dim3(128), rsm, (const float *)Y.A2_32, (const ly::bf16 *)L.w_router, n, E, X, top, rpc, Y.moe_ids, Y.moe_wts, rm, 0, (float *)nullptr);
                 if (rc) return rc;
                 nl++;
             }
@@ -310,7 +311,7 @@ static int ly_enqueue_parallel(b200_plan *p, bool decode, int n, const StepState
                 int t128 = (n * top + 127) / 128 + X;
                 if (t128 > Y.max_tiles128) t128 = Y.max_tiles128;
                 if ((rc = launch_k(p, false, ly::k_moe_group_padded, dim3(1), dim3(1024), (size_t)3 * X * 4, (const int *)Y.moe_ids, (const float *)Y.moe_wts, n * top, X, t128, Y.srt, Y.slot_row,
-                                   Y.row_scale, Y.tile_group128))) return rc;
+                                   Y.row_scale, Y.tile_group128, X, 0))) return rc;
                 if ((rc = launch_k(p, false, ly::k_moe_gather, dim3(t128 * 128), dim3(128), (size_t)0, (const ly::bf16 *)Y.A2_16, E, top, (const int *)Y.srt, (const int *)Y.tile_group128, Y.AS16))) return rc;
                 const uint32_t fl = pg::FLAVOR_BF16 | (s.ff_act == B200_ACT_SILU ? pg::FLAVOR_SILU_BF16 : pg::FLAVOR_GELU_BF16);
                 int gr = pg::gemm_launch<pg::GEMM_GATEUP, pg::GEMM_STAGES>(Y.m_as, L.m_moe_gate, L.m_moe_up, Y.m_ysp, Y.HS16, F, t128 * 128, t128, F / (pg::BN / 2), E, p->stream, fl,
@@ -327,7 +328,7 @@ static int ly_enqueue_parallel(b200_plan *p, bool decode, int n, const StepState
             if (!decode) {
                 tiles = (n * top + 63) / 64 + X;
                 if (tiles > Y.max_tiles) tiles = Y.max_tiles;
-                if ((rc = launch_k(p, false, ly::k_moe_group, dim3(1), dim3(1024), (size_t)3 * X * 4, (const int *)Y.moe_ids, n * top, X, tiles, Y.moe_perm, Y.tile_group, Y.tile_row0, Y.tile_rows))) return rc;
+                if ((rc = launch_k(p, false, ly::k_moe_group, dim3(1), dim3(1024), (size_t)3 * X * 4, (const int *)Y.moe_ids, n * top, X, tiles, Y.moe_perm, Y.tile_group, Y.tile_row0, Y.tile_rows, X))) return rc;
                 nl++;
             }
             ly::GemmView gv{};

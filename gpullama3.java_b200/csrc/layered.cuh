@@ -25,8 +25,8 @@ namespace ly {
 
 typedef __nv_bfloat16 bf16;
 
-enum { EPI_STORE = 0, EPI_GATED = 1 };   // C = A W^T (+ bias)  |  H = act(A Wg^T) * (A Wu^T) with W = [Wg; Wu] stacked by rows
-enum { ACT_GELU_TANH = 0, ACT_SILU = 1, ACT_RELU = 2 };
+enum { EPI_STORE = 0, EPI_GATED = 1, EPI_ACT = 2 }; // C = A W^T (+ bias)  |  H = act(A Wg^T) * (A Wu^T), W = [Wg; Wu] stacked by rows  |  H = act(A W^T (+ bias))
+enum { ACT_GELU_TANH = 0, ACT_SILU = 1, ACT_RELU = 2, ACT_GELU_ERF = 3 };
 
 __device__ __forceinline__ float bf_lo(unsigned v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf_hi(unsigned v) { return __uint_as_float(v & 0xffff0000u); }
@@ -34,6 +34,7 @@ __device__ __forceinline__ float bf_hi(unsigned v) { return __uint_as_float(v & 
 __device__ __forceinline__ float act_apply(int act, float z) {
     if (act == ACT_SILU) return z / (1.0f + expf(-z));
     if (act == ACT_RELU) return fmaxf(z, 0.0f);
+    if (act == ACT_GELU_ERF) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f)); // the exact GELU: z * Phi(z)
     // tanh form of GELU: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
     const float u = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
     return 0.5f * z * (1.0f + tanhf(u));
@@ -185,6 +186,7 @@ struct MvView {
     long long w_gs;
     const float *in_scale;
     const float *mul;
+    int n_groups; // > 0: a CTA whose group[b] >= n_groups has nothing to do (an expert without weights: the identity)
 };
 
 template <int EPI>
@@ -192,6 +194,7 @@ __global__ void __launch_bounds__(LY_MV_THREADS) k_matvec_bf16(const bf16 *__res
                                                               float *__restrict__ y, int N, int K, int act, MvView v_) {
     extern __shared__ __align__(16) float xs[];
     const int b = blockIdx.y;
+    if (v_.group && v_.n_groups > 0 && v_.group[b] >= v_.n_groups) return;
     W += (size_t)b * v_.w_bs + (v_.group ? (size_t)v_.group[b] * v_.w_gs : (size_t)0);
     x += (size_t)b * v_.x_bs;
     y += (size_t)b * v_.y_bs;
@@ -205,6 +208,9 @@ __global__ void __launch_bounds__(LY_MV_THREADS) k_matvec_bf16(const bf16 *__res
         if (EPI == EPI_GATED) {
             const float u = dot_row_bf16(W + (size_t)(N + n) * K, xs, K, lane, vec);
             v = act_apply(act, v * sc) * (u * sc);
+        } else if (EPI == EPI_ACT) {
+            if (bias) v += bias[n];
+            v = act_apply(act, v);
         } else {
             if (bias) v += bias[n];
             if (v_.mul) v *= 1.0f / (1.0f + expf(-v_.mul[(size_t)b * v_.y_bs + n]));
@@ -263,6 +269,7 @@ __device__ __forceinline__ float gemm_epilogue(const GemmView &g, float a0, floa
         const float sc = g.in_scale ? g.in_scale[crow] : 1.0f;
         return act_apply(act, a0 * sc) * (a1 * sc);
     }
+    if (EPI == EPI_ACT) return act_apply(act, a0 + (bias ? bias[n] : 0.0f));
     float v = a0 + (bias ? bias[n] : 0.0f);
     if (g.mul) v *= 1.0f / (1.0f + expf(-g.mul[(size_t)crow * g.ldmul + c_off + n]));
     return v;
@@ -467,6 +474,9 @@ struct WindowAttn {
     const float *gate_src;       // the gate is read from row r of this buffer (row stride gate_ld) instead of the query's row (nullable)
     int gate_ld;
     int gate_heads;              // 1: ONE gate per head (g has `heads` entries) instead of one per output entry
+    int maps;                    // > 1: every head carries `maps` score maps over the same values.  `heads` then counts (head, map) pairs, pair
+                                 // p = head * maps + map reads key slice (value head) * maps + map of a key row [kv_heads][maps][dk] and the
+                                 // values of its head; the output keeps one row of dv entries per pair
 };
 // Row layout of the fused projection output: [q: heads*dk | k: kv_heads*dk | v: kv_heads*dv | g: heads*dv]
 
@@ -533,7 +543,7 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
     const int splits = gridDim.z, z = blockIdx.z;
     const int qd = a.heads * a.dk, kd = a.kv_heads * a.dk, vd = a.kv_heads * a.dv;
     const int g = h / (a.heads / a.kv_heads);
-    const int gk = a.k_heads > 0 ? h / (a.heads / a.k_heads) : g;
+    const int gk = a.maps > 1 ? g * a.maps + h % a.maps : a.k_heads > 0 ? h / (a.heads / a.k_heads) : g;
     const float sink_v = a.sink_logit ? a.sink_logit[h] : 0.0f;
     const int pos = st->pos + r;
     int lo = pos - a.window + 1 > 0 ? pos - a.window + 1 : 0;
@@ -711,7 +721,7 @@ __device__ __forceinline__ void ldmatrix_x2_trans(unsigned (&r)[2], const void *
 template <int DK, int DV>
 __global__ void __launch_bounds__(LY_ATT_MMA_THREADS) k_window_attention_mma(const float *__restrict__ P, int ldp, WindowAttn a, const bf16 *__restrict__ kc16,
                                                                              const bf16 *__restrict__ vc16, const StepState *__restrict__ st, int n,
-                                                                             bf16 *__restrict__ out, int ldo) {
+                                                                             bf16 *__restrict__ out, int ldo, float *__restrict__ out32 = nullptr) {
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr int BM = LY_ATT_MMA_ROWS;
     constexpr int QT = BM * (DK + 8) * 2, KT = 64 * (DK + 8) * 2, VT = 64 * (DV + 8) * 2; // bytes of the Q tile, one K tile, one V tile
@@ -721,7 +731,7 @@ __global__ void __launch_bounds__(LY_ATT_MMA_THREADS) k_window_attention_mma(con
     const int h = blockIdx.y, r0 = blockIdx.x * BM;
     const int kd = a.ldk, vd = a.ldv, qd = a.heads * DK; // row strides of the BF16 twin rings = those of the FP32 rings
     const int kvh = h / (a.heads / a.kv_heads);
-    const int kh = a.k_heads > 0 ? h / (a.heads / a.k_heads) : kvh;
+    const int kh = a.maps > 1 ? kvh * a.maps + h % a.maps : a.k_heads > 0 ? h / (a.heads / a.k_heads) : kvh;
     const float sink_v = a.sink_logit ? a.sink_logit[h] : 0.0f;
     const int pos0 = st->pos;
     const int rows = n - r0 < BM ? n - r0 : BM;
@@ -889,7 +899,8 @@ __global__ void __launch_bounds__(LY_ATT_MMA_THREADS) k_window_attention_mma(con
                 v0 *= 1.0f / (1.0f + expf(-gv.x));
                 v1 *= 1.0f / (1.0f + expf(-gv.y));
             }
-            *reinterpret_cast<unsigned *>(out + (size_t)r * ldo + (size_t)h * DV + d) = pack_bf16(v0, v1);
+            if (out32) *reinterpret_cast<float2 *>(out32 + (size_t)r * ldo + (size_t)h * DV + d) = make_float2(v0, v1); // FP32 results (what a later subtraction reads)
+            else *reinterpret_cast<unsigned *>(out + (size_t)r * ldo + (size_t)h * DV + d) = pack_bf16(v0, v1);
         }
     }
 }

@@ -26,6 +26,7 @@
 #include "layered.cuh"
 #include "latent.cuh"
 #include "delta.cuh"
+#include "recurrent.cuh"
 
 struct LyLayer {
     b200_layer_spec s{};
@@ -64,6 +65,16 @@ struct LyLayer {
     // gated delta rule: convolution weights of the q | k | v channels, per-head constants, weight of the read-out norm
     float *conv_w = nullptr, *a_log = nullptr, *dt_bias = nullptr, *onorm = nullptr;
     int dC = 0; // convolved channels = 2 * kv_heads * key_dim + heads * value_dim
+    // OUTNORM block: token shift, depth average weights; differential attention; recurrent unit (stacked gate matrices [blocks][r | i rows][in],
+    // their biases, branch biases); state-space recurrence; mixture of experts with correction and a shared expert; plain feed-forward (w_gu = up)
+    float *shift = nullptr, *dwa = nullptr;
+    float diff_lambda = 0.0f;
+    ly::bf16 *w_gates = nullptr;
+    float *gate_bias = nullptr, *lam = nullptr, *x_bias = nullptr, *y_bias = nullptr, *conv_b = nullptr, *ssd_d = nullptr;
+    float *correction = nullptr;
+    ly::bf16 *w_sgu = nullptr, *w_sdown = nullptr;
+    CUtensorMap m_sgate, m_sup, m_sdown, m_sh;
+    bool tc_sgu = false, tc_sdown = false;
 };
 struct LyRun {
     int layer = 0, pass = -1;
@@ -75,6 +86,8 @@ struct LyRun {
     int kw = 0, vw = 0;                        // floats per cache row (latent attention: one cache, kw = kv_rank + rot_dim, vc == nullptr)
     bool own = true;                           // false: kc is the cache of the run this layer reads (kv_from)
     float *S = nullptr, *cstate = nullptr;     // gated delta rule: state [heads][key_dim][value_dim]; ring of convolution inputs [cring][channels]
+    size_t s_floats = 0, c_floats = 0;         // sizes of S and cstate
+    float *prev = nullptr;                     // token shift: the row the run's mixer read last, before its shift
 };
 struct Layered {
     b200_layered_config c{};
@@ -119,6 +132,12 @@ struct Layered {
     float *emb_norm = nullptr;
     float *DLT = nullptr, *DO = nullptr; // prepared q | k | v | beta | decay rows and read-out rows of a delta layer, [cap][...]
     int maxD = 0, maxDO = 0, cring = 0, max_taps = 0;
+    // OUTNORM block: kept layer results X_j [layers + 1][cap][width], the shared expert's result, its gate logits, BF16 twin of a convolved row
+    bool outnorm = false;
+    float *STASH = nullptr, *SH = nullptr, *SGL = nullptr;
+    ly::bf16 *U16 = nullptr;
+    int max_att_heads = 1;
+    CUtensorMap m_sh_c;
 };
 
 // What ly_project needs to take the tcgen05 route: operand and result descriptors (nullptr = CUDA-core / mma.sync kernels).
@@ -204,14 +223,14 @@ static size_t ly_mma_smem(int kind, int window) {
          : kind == 4 ? ly::att_mma_smem_bytes<128, 64>(window) : ly::att_mma_smem_bytes<256, 128>(window);
 }
 static int ly_launch_mma(b200_plan *p, int kind, int n, int heads, int window, const float *P, int ldp, const ly::WindowAttn &wa, const ly::bf16 *k16, const ly::bf16 *v16,
-                         const StepState *st, ly::bf16 *out, int ldo) {
+                         const StepState *st, ly::bf16 *out, int ldo, float *out32 = nullptr) {
     const dim3 grid((n + LY_ATT_MMA_ROWS - 1) / LY_ATT_MMA_ROWS, heads), block(LY_ATT_MMA_THREADS);
     const size_t sm = ly_mma_smem(kind, window);
-    if (kind == 1) return launch_k(p, false, ly::k_window_attention_mma<64, 64>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
-    if (kind == 2) return launch_k(p, false, ly::k_window_attention_mma<128, 128>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
-    if (kind == 4) return launch_k(p, false, ly::k_window_attention_mma<128, 64>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
-    if (kind == 5) return launch_k(p, false, ly::k_window_attention_mma<256, 128>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
-    return launch_k(p, false, ly::k_window_attention_mma<192, 128>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
+    if (kind == 1) return launch_k(p, false, ly::k_window_attention_mma<64, 64>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo, out32);
+    if (kind == 2) return launch_k(p, false, ly::k_window_attention_mma<128, 128>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo, out32);
+    if (kind == 4) return launch_k(p, false, ly::k_window_attention_mma<128, 64>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo, out32);
+    if (kind == 5) return launch_k(p, false, ly::k_window_attention_mma<256, 128>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo, out32);
+    return launch_k(p, false, ly::k_window_attention_mma<192, 128>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo, out32);
 }
 
 static ly::WindowAttn ly_attn_args(const Layered &Y, const LyLayer &L) {
@@ -272,12 +291,14 @@ static int ly_project(b200_plan *p, bool decode, int n, const float *a32, const 
 }
 
 #include "latent_plan.cuh"
+#include "outnorm_plan.cuh"
 
 // Enqueue the forward of n rows on p->stream.  decode: the single-token step (row 0, position and token from *st).
 // with_head (decode only): final norm + classifier into p->logits.  Prefill leaves the finished residual rows in X.
 static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, const int *tokens, bool with_head, float *trace, int *launches) {
     Layered &Y = *p->ly;
     if (Y.c.block == B200_BLOCK_PARALLEL) return ly_enqueue_parallel(p, decode, n, st, tokens, with_head, trace, launches);
+    if (Y.c.block == B200_BLOCK_OUTNORM) return ly_enqueue_outnorm(p, decode, n, st, tokens, with_head, trace, launches);
     const int E = Y.c.width;
     const bool h16 = !decode && !Y.f32; // prefill in BF16 mode rounds GEMM operands to BF16
     int nl = 0, rc;
@@ -424,6 +445,7 @@ static int ly_tc_init(b200_plan *p) {
         const int F = L.s.ff_dim;
         L.tc_proj = fits(L.P, E) && Y.maxP % 4 == 0 && pg::make_map(&L.m_proj, L.w_proj, L.P, E, 128) == 0;
         L.tc_o = fits(E, L.gd) && pg::make_map(&L.m_o, L.w_o, E, L.gd, 128) == 0 && pg::make_map(&L.m_att, Y.ATT16, rows, L.gd, pg::BM) == 0;
+        if (Y.outnorm) continue; // its feed-forwards: ly_outnorm_tc_init
         if (L.w_gu && L.s.ff_kind == B200_FF_DENSE_GATED) {
             L.tc_gu = fits(F, E) && pg::make_map(&L.m_gate, L.w_gu, F, E, 128) == 0 &&
                       pg::make_map(&L.m_up, L.w_gu + (size_t)F * E, F, E, 128) == 0;
@@ -451,6 +473,7 @@ static int ly_tc_init(b200_plan *p) {
             L.tc_moe = pg::make_map(&L.m_moe_gate, L.w_gu, X * 2 * F, E, pg::BN / 2) == 0 && pg::make_map(&L.m_moe_up, L.w_gu + F * E, X * 2 * F - F, E, pg::BN / 2) == 0 &&
                        pg::make_map(&L.m_moe_down, L.w_down, X * E, F, pg::BN) == 0 && pg::make_map(&L.m_moe_h, Y.HS16, (uint64_t)Y.max_tiles128 * 128, F, pg::BM) == 0;
         }
+    if (Y.outnorm) ly_outnorm_tc_init(p);
     Y.tc_head = fits(V, E) && pg::make_map(&Y.m_head, Y.head, V, E, 128) == 0 && pg::make_map_c(&Y.m_log_c, Y.LOG, 256, V) == 0;
     Y.tc = true;
     return B200_OK;
@@ -462,8 +485,15 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     Layered &Y = *Yp;
     Y.c = *cfg;
     const b200_layered_config &c = Y.c;
-    if (c.arch != B200_ARCH_PIBIDRA && c.arch != B200_ARCH_LATUSUN && c.arch != B200_ARCH_LEROSUN) return fail(p, B200_ERR_UNSUPPORTED, "unknown layered arch %d", c.arch);
-    if (c.block != B200_BLOCK_SANDWICH && c.block != B200_BLOCK_PARALLEL && c.block != B200_BLOCK_PRENORM) return fail(p, B200_ERR_BAD_ARG, "unknown block kind %d", c.block);
+    if (c.arch != B200_ARCH_PIBIDRA && c.arch != B200_ARCH_LATUSUN && c.arch != B200_ARCH_LEROSUN && c.arch != B200_ARCH_DINUZEN) return fail(p, B200_ERR_UNSUPPORTED, "unknown layered arch %d", c.arch);
+    if (c.block != B200_BLOCK_SANDWICH && c.block != B200_BLOCK_PARALLEL && c.block != B200_BLOCK_PRENORM && c.block != B200_BLOCK_OUTNORM) return fail(p, B200_ERR_BAD_ARG, "unknown block kind %d", c.block);
+    Y.outnorm = c.block == B200_BLOCK_OUTNORM;
+    const bool outn = Y.outnorm;
+    if (outn) {
+        if (c.loop_times >= 0 && c.loop_stop > c.loop_start) return fail(p, B200_ERR_UNSUPPORTED, "blocks with the norm on the sublayer's output do not loop");
+        if (Y.c.norm_groups <= 0) Y.c.norm_groups = 1;
+        if (c.width % Y.c.norm_groups || Y.c.norm_groups > LY_OUTNORM_MAX_GROUPS) return fail(p, B200_ERR_BAD_ARG, "width %d in %d norm groups", c.width, Y.c.norm_groups);
+    }
     Y.prenorm = c.block == B200_BLOCK_PRENORM;
     Y.w_off = Y.prenorm ? 0.0f : 1.0f;
     const bool par = c.block == B200_BLOCK_PARALLEL;
@@ -498,6 +528,10 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         L.s = specs[l];
         if (L.s.window > c.context_length) L.s.window = c.context_length; // no position is further back than the context: same result, smaller tables
         const b200_layer_spec &s = L.s;
+        if (outn) {
+            if ((rc = ly_outnorm_sizes(p, l, L, specs))) return rc;
+            continue;
+        }
         if (par) {
             // parallel block: latent attention and a mixture of experts (or no feed-forward)
             if (s.mixer != B200_MIXER_LATENT_ATTENTION) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: mixer %d in a parallel block", l, s.mixer);
@@ -572,6 +606,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if (Y.maxF > maxK) maxK = Y.maxF;
         for (const LyLayer &L : Y.layers) if (L.s.kv_rank > maxK) maxK = L.s.kv_rank; // reduction width of the per-head value expansion
         size_t need = (size_t)maxK * 4;
+        if (outn && (size_t)2 * E * 4 > need) need = (size_t)2 * E * 4; // the row kernel holds the row and the sublayer's output
         for (const LyLayer &L : Y.layers) if (ly_att_smem(L.s, 0) > need) need = ly_att_smem(L.s, 0);
         if (need > (size_t)Y.smem_max) return fail(p, B200_ERR_UNSUPPORTED, "a row of %zu bytes (widest activation or window) exceeds the %d bytes of shared memory a CTA can hold", need, Y.smem_max);
         static bool attrs = false; // per function and process-wide, like plan.cu's set_smem_attrs
@@ -592,6 +627,9 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             CK(set_max_dyn(ly::k_delta_prep, Y.smem_max));
             CK(set_max_dyn(ly::k_rope_mix_prep, Y.smem_max));
             CK(set_max_dyn(ly::k_delta_rule, Y.smem_max));
+            CK(set_max_dyn(ly::k_outnorm_rows, Y.smem_max));
+            CK(set_max_dyn(ly::k_gated_group_norm, Y.smem_max));
+            CK(set_max_dyn(ly::k_matvec_bf16<ly::EPI_ACT>, Y.smem_max));
             attrs = true;
         }
     }
@@ -632,7 +670,9 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     if ((rc = ly_mat(p, tensors, nt, "embed", c.vocab_size, E, Y.emb, 0))) return rc;
     if ((rc = dalloc(p, &Y.head, (size_t)c.vocab_size * E * 2))) return rc;
     if ((rc = ly_mat(p, tensors, nt, "head", c.vocab_size, E, Y.head, 0))) return rc;
-    if (Y.prenorm) {
+    if (outn) {
+        if ((rc = ly_vec_f32(p, tensors, nt, "final.norm", E, &Y.final_norm))) return rc;
+    } else if (Y.prenorm) {
         if ((rc = ly_scalar_vec(p, tensors, nt, "final.norm", E, &Y.final_norm))) return rc;
         if ((rc = ly_scalar_vec(p, tensors, nt, "embed.norm", E, &Y.emb_norm))) return rc;
     } else if ((rc = ly_vec_f32(p, tensors, nt, "final.norm", E, &Y.final_norm))) return rc;
@@ -645,6 +685,10 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         const std::string pre = "l" + std::to_string(l) + ".", mx = pre + "mix.", ff = pre + "mlp.";
         if (par) {
             if ((rc = ly_latent_upload(p, l, L, tensors, nt))) return rc;
+            continue;
+        }
+        if (outn) {
+            if ((rc = ly_outnorm_upload(p, l, L, tensors, nt))) return rc;
             continue;
         }
         if (Y.prenorm) {
@@ -741,6 +785,10 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     Y.cring = Y.max_taps > 0 ? Y.max_taps - 1 + Y.cap : 0;
     for (LyRun &R : Y.runs) {
         const LyLayer &L = Y.layers[R.layer];
+        if (outn) {
+            if ((rc = ly_outnorm_run(p, R, L))) return rc;
+            continue;
+        }
         if (L.s.mixer == B200_MIXER_LATENT_ATTENTION) {
             // one cache of [latent | rotated shared key part] rows; a layer that reads another layer's cache points at it (runs = layers here)
             R.kw = L.kw;
@@ -756,6 +804,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if (L.s.mixer == B200_MIXER_GATED_DELTA) {
             // the run's recurrent state and its ring of convolution inputs (position j in slot j % cring)
             const size_t sb = ly::delta_state_floats(L.s.heads, L.s.key_dim, L.s.value_dim) * 4, cb = (size_t)Y.cring * L.dC * 4;
+            R.s_floats = sb / 4; R.c_floats = cb / 4;
             if ((rc = dalloc(p, &R.S, sb))) return rc;
             if ((rc = dalloc(p, &R.cstate, cb))) return rc;
             CK(cudaMemset(R.S, 0, sb));
@@ -785,7 +834,13 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     if ((rc = dalloc(p, &Y.X, cap * E * 4))) return rc;
     if (Y.has_loop && !Y.prenorm && (rc = dalloc(p, &Y.X0, cap * E * 4))) return rc;
     if (!par && Y.maxQ > 0 && (rc = dalloc(p, &Y.Q, cap * Y.maxQ * 4))) return rc;
-    if (Y.maxD > 0 && ((rc = dalloc(p, &Y.DLT, cap * Y.maxD * 4)) || (rc = dalloc(p, &Y.DO, cap * Y.maxDO * 4)))) return rc;
+    if (outn) {
+        if (Y.c.depth_average && (rc = dalloc(p, &Y.STASH, (size_t)(c.n_layers + 1) * Y.cap * E * 4))) return rc;
+        if (Y.maxTop > 0 && ((rc = dalloc(p, &Y.SH, cap * E * 4)) || (rc = dalloc(p, &Y.SGL, cap * 4)))) return rc;
+        if (!Y.f32 && Y.maxD > 0 && (rc = dalloc(p, &Y.U16, cap * Y.maxD * 2))) return rc;
+        if (Y.maxDO > 0 && !Y.DO && (rc = dalloc(p, &Y.DO, cap * Y.maxDO * 4))) return rc;
+    }
+    if (Y.maxD > 0 && ((rc = dalloc(p, &Y.DLT, cap * Y.maxD * 4)) || (rc = dalloc(p, &Y.DO, cap * (Y.maxDO > 0 ? Y.maxDO : 1) * 4)))) return rc;
     if ((rc = dalloc(p, &Y.Y, cap * E * 4))) return rc;
     if ((rc = dalloc(p, &Y.PROJ, cap * Y.maxP * 4))) return rc;
     if ((rc = dalloc(p, &Y.A32, rows32 * E * 4))) return rc;
@@ -796,7 +851,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if ((rc = dalloc(p, &Y.ATT16, cap * Y.maxO * 2))) return rc;
         if ((rc = dalloc(p, &Y.H16, cap * slots * maxF * 2))) return rc;
     }
-    if (par) {
+    if (par || outn) {
         if (Y.maxKX > 0) {
             if ((rc = dalloc(p, &Y.KX16, (size_t)Y.ring * Y.maxKX * 2))) return rc;
             if ((rc = dalloc(p, &Y.VX16, (size_t)Y.ring * Y.maxVX * 2))) return rc;
@@ -804,10 +859,10 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             if ((rc = dalloc(p, &Y.KXF, rowsX * Y.maxKX * 4))) return rc;
             if ((rc = dalloc(p, &Y.VXF, rowsX * Y.maxVX * 4))) return rc;
         }
-        if ((rc = dalloc(p, &Y.A2_32, rows32 * E * 4))) return rc;
-        if ((rc = dalloc(p, &Y.Q, cap * Y.maxQ * 4))) return rc;
-        if ((rc = dalloc(p, &Y.LAT32, rows32 * Y.maxL * 4))) return rc;
-        if (!Y.f32) {
+        if (par && (rc = dalloc(p, &Y.A2_32, rows32 * E * 4))) return rc;
+        if (par && (rc = dalloc(p, &Y.Q, cap * Y.maxQ * 4))) return rc;
+        if (par && (rc = dalloc(p, &Y.LAT32, rows32 * Y.maxL * 4))) return rc;
+        if (par && !Y.f32) {
             if ((rc = dalloc(p, &Y.A2_16, cap * E * 2))) return rc;
             if ((rc = dalloc(p, &Y.QU16, cap * Y.maxQU * 2))) return rc;
             if ((rc = dalloc(p, &Y.LAT16, cap * Y.maxL * 2))) return rc;
@@ -845,6 +900,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if (e && atoi(e) >= 1) Y.max_splits = atoi(e) > 8 ? 8 : atoi(e);
         int maxH = 1, maxdv = Y.max_att_dv;
         for (const LyLayer &L : Y.layers) if (L.s.heads > maxH) maxH = L.s.heads;
+        if (Y.max_att_heads > maxH) maxH = Y.max_att_heads;
         if (Y.max_splits > 1) {
             if ((rc = dalloc(p, &Y.split.o, (size_t)maxH * Y.max_splits * maxdv * 4))) return rc;
             if ((rc = dalloc(p, &Y.split.ml, (size_t)maxH * Y.max_splits * 2 * 4))) return rc;
@@ -906,7 +962,12 @@ static int ly_batch(b200_plan *p, const int32_t *tokens, int n, int start_pos, c
         const int m = n_rows - r0 < Y.logit_rows ? n_rows - r0 : Y.logit_rows;
         memcpy(p->h_ids, rows + r0, (size_t)m * 4);
         CK(cudaMemcpyAsync(Y.rows, p->h_ids, (size_t)m * 4, cudaMemcpyHostToDevice, p->stream));
-        if (Y.c.block == B200_BLOCK_PARALLEL) {
+        if (Y.outnorm) {
+            ly::OutNormArgs a = ly_outnorm_args(Y, m);
+            a.w_out = Y.final_norm; a.gather = Y.rows; a.st = Y.st_pf;
+            a.out32 = Y.f32 ? Y.A32 : nullptr; a.out16 = Y.f32 ? nullptr : Y.A16;
+            if ((rc = launch_k(p, false, ly::k_outnorm_rows, dim3(m), dim3(LY_NORM_THREADS), (size_t)2 * E * 4, a))) return rc;
+        } else if (Y.c.block == B200_BLOCK_PARALLEL) {
             ly::BlockNormArgs a = ly_block_norm_args(Y);
             a.w1 = Y.final_norm; a.b1 = Y.final_norm_b; a.gather = Y.rows;
             a.out1_32 = Y.f32 ? Y.A32 : nullptr; a.out1_16 = Y.f32 ? nullptr : Y.A16;
@@ -935,10 +996,10 @@ static int ly_kv_reset(b200_plan *p) {
     Layered &Y = *p->ly;
     for (LyRun &R : Y.runs) {
         if (R.S) {
-            const LyLayer &L = Y.layers[R.layer];
-            CK(cudaMemsetAsync(R.S, 0, ly::delta_state_floats(L.s.heads, L.s.key_dim, L.s.value_dim) * 4, p->stream));
-            CK(cudaMemsetAsync(R.cstate, 0, (size_t)Y.cring * L.dC * 4, p->stream));
+            CK(cudaMemsetAsync(R.S, 0, R.s_floats * 4, p->stream));
+            CK(cudaMemsetAsync(R.cstate, 0, R.c_floats * 4, p->stream));
         }
+        if (R.prev) CK(cudaMemsetAsync(R.prev, 0, (size_t)Y.c.width * 4, p->stream));
         if (!R.own || !R.kc) continue;
         CK(cudaMemsetAsync(R.kc, 0, (size_t)Y.ring * R.kw * 4, p->stream));
         if (R.vc) CK(cudaMemsetAsync(R.vc, 0, (size_t)Y.ring * R.vw * 4, p->stream));
@@ -963,9 +1024,8 @@ static int ly_read_buffer(b200_plan *p, const char *name, int layer, void *dst, 
         if (!src) return fail(p, B200_ERR_BAD_ARG, "run %d has no %s", layer, name);
     } else if (s == "delta_state" || s == "conv_state") {
         if (layer < 0 || layer >= (int)Y.runs.size() || !Y.runs[layer].S) return fail(p, B200_ERR_BAD_ARG, "run %d has no %s", layer, name);
-        const LyLayer &L = Y.layers[Y.runs[layer].layer];
         src = s == "delta_state" ? Y.runs[layer].S : Y.runs[layer].cstate;
-        sz = s == "delta_state" ? ly::delta_state_floats(L.s.heads, L.s.key_dim, L.s.value_dim) * 4 : (size_t)Y.cring * L.dC * 4;
+        sz = (s == "delta_state" ? Y.runs[layer].s_floats : Y.runs[layer].c_floats) * 4;
     } else return fail(p, B200_ERR_BAD_ARG, "unknown buffer %s", name);
     if (bytes < sz) sz = bytes;
     CK(cudaSetDevice(p->device));
@@ -986,6 +1046,10 @@ static int ly_time_kernel(b200_plan *p, int which, int reps, float *avg_ms, int6
     auto one = [&](const LyLayer *L) -> int {
         switch (which) {
         case 0: if (!L->w_gu) return B200_OK; bytes = (int64_t)2 * L->s.ff_dim * E * 2; launches++;
+                if (L->s.ff_kind == B200_FF_DENSE_PLAIN) { // one matrix, activation in the epilogue
+                    bytes /= 2;
+                    return ly_project<ly::EPI_ACT>(p, true, 1, Y.A32, nullptr, L->w_gu, nullptr, L->s.ff_dim, E, Y.H32, nullptr, L->s.ff_dim, L->s.ff_act);
+                }
                 return ly_project<ly::EPI_GATED>(p, true, 1, Y.A32, nullptr, L->w_gu, nullptr, L->s.ff_dim, E, Y.H32, nullptr, L->s.ff_dim, L->s.ff_act);
         case 1: if (!L->w_down) return B200_OK; bytes = (int64_t)L->s.ff_dim * E * 2; launches++;
                 return ly_project<ly::EPI_STORE>(p, true, 1, Y.H32, nullptr, L->w_down, nullptr, E, L->s.ff_dim, Y.Y, nullptr, E, 0);

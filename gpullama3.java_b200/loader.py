@@ -24,6 +24,7 @@ ARCH_PHI3 = 2
 ARCH_PIBIDRA = 3
 ARCH_LATUSUN = 4
 ARCH_LEROSUN = 5
+ARCH_DINUZEN = 6
 
 GGML_BF16 = 30  # ggml's id for bfloat16; layered plans take their safetensors tensors under it
 _SAFETENSORS_TYPES = {"BF16": GGML_BF16, "F16": GGMLType.F16, "F32": GGMLType.F32}
@@ -92,6 +93,18 @@ class LayerSpec:
     head_mix: bool = False      # scores mixed over the query heads before the softmax
     # gated delta rule: heads = value heads, kv_heads = query / key heads
     conv_taps: int = 0
+    # differential attention (two score maps per head over the same values) and a per-slice q/k norm with one weight of size key_dim
+    score_maps: int = 1
+    diff_init: float = 0.0
+    qk_head_norm: bool = False
+    # "rglru": heads = diagonal blocks of the gates, value_dim = channels per block; "ssd": heads x value_dim values, key_dim = state
+    # size, kv_heads = groups of B and C; mixer_norm_groups = parts of the read-out norm
+    mixer_norm_groups: int = 1
+    # mixture of experts
+    moe_router: str = "sigmoid_input"   # | "softmax_output": softmax scores, selection by score + correction, weights on the outputs
+    moe_identity: int = 0               # identity experts behind the real ones
+    moe_scale: float = 1.0
+    moe_shared_ff: int = 0              # width of the shared expert (0: none)
 
 
 @dataclass
@@ -111,6 +124,10 @@ class LayeredConfiguration:
     block: str = "sandwich"
     residual_mult: float = 1.0
     logit_softcap: float = 0.0
+    # "outnorm": x += s1 * GN(mixer(shift x)); x += s2 * GN(ff(x)), GN = RMS norm in norm_groups parts on the sublayer's output
+    norm_groups: int = 1
+    token_shift: bool = False
+    depth_average: bool = False
 
     @property
     def n_layers(self):
@@ -265,9 +282,56 @@ def lerosun_configuration(cfg: dict, tensor_shapes: dict, context_length: int) -
         (int(loop["start"]), int(loop["stop"]), int(loop["times"])) if loop else None, block="prenorm")
 
 
+def dinuzen_configuration(cfg: dict, tensor_shapes: dict, context_length: int) -> LayeredConfiguration:
+    """config.json of a Dinuzen model -> LayeredConfiguration: blocks with the norm on the sublayer's output, token shift and depth
+    average; per layer a real-gated linear recurrent unit, a state-space recurrence or a differential attention, and a plain GELU
+    feed-forward or a softmax-routed mixture of experts.  Every size and every constant that can differ between models comes from
+    the file."""
+    layers = []
+    for i, lc in enumerate(cfg["layers"]):
+        m, mlp = lc["mixer"], lc.get("mlp")
+        if mlp is None:
+            ff = dict(ff_dim=0)
+        elif mlp.get("kind") == "dense":
+            ff = dict(ff_dim=int(mlp["ff"]), ff_act="gelu_erf", ff_kind="dense_plain")
+        elif mlp.get("kind") == "moe":
+            r, sh = mlp["router"], mlp.get("shared")
+            ff = dict(ff_dim=int(mlp["expert"]["ff"]), ff_act="silu", ff_kind="moe", ff_experts=int(r["experts"]), ff_top=int(r["top"]),
+                      moe_router="softmax_output", moe_identity=int(r.get("identity", 0)), moe_scale=float(r.get("scale", 1.0)),
+                      moe_shared_ff=int(sh["ff"]) if sh else 0)
+        else:
+            raise UnsupportedModel(f"layer {i}: feed-forward kind {mlp.get('kind')!r}")
+        base = dict(bias_rows=0, bias_far=0.0, sink=False, gate=False, qkv_bias=False, qk_norm=False)
+        if lc["type"] == "attention":
+            rot = m["rot"]
+            sc = rot.get("scaling")
+            kv_from = m.get("kv_from")
+            if kv_from is not None and f"l{i}.mix.k" in tensor_shapes:
+                raise UnsupportedModel(f"layer {i}: reads layer {kv_from}'s keys and values but carries projections of its own")
+            layers.append(LayerSpec(
+                heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), key_dim=int(m["dim"]), value_dim=int(m["vdim"]), window=int(context_length),
+                score_scale=float(m["scale"]), softcap=float(m.get("softcap") or 0.0), score_maps=2, diff_init=float(m["diff"]), qk_head_norm=True,
+                kv_from=-1 if kv_from is None else int(kv_from), rope_dims=int(rot["dims"]), rope_layout="interleaved", rope_base=float(rot["base"]),
+                yarn=(float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"])) if sc else (0.0, 0.0, 0.0, 0.0), **base, **ff))
+        elif lc["type"] == "rglru":
+            blocks, width = int(m["blocks"]), int(m["width"])
+            if blocks <= 0 or width % blocks:
+                raise UnsupportedModel(f"layer {i}: {width} channels in {blocks} blocks")
+            layers.append(LayerSpec(heads=blocks, kv_heads=blocks, key_dim=width // blocks, value_dim=width // blocks, window=1, score_scale=1.0, softcap=0.0,
+                                    mixer="rglru", conv_taps=int(m["conv"]), **base, **ff))
+        elif lc["type"] == "mamba2":
+            layers.append(LayerSpec(heads=int(m["heads"]), kv_heads=int(m["groups"]), key_dim=int(m["state"]), value_dim=int(m["vdim"]), window=1, score_scale=1.0,
+                                    softcap=0.0, mixer="ssd", conv_taps=int(m["conv"]), mixer_norm_groups=int(m.get("norm_groups", 1)), **base, **ff))
+        else:
+            raise UnsupportedModel(f"layer {i}: mixer type {lc['type']!r} (Dinuzen layers are 'attention', 'rglru' or 'mamba2')")
+    return LayeredConfiguration(
+        ARCH_DINUZEN, int(cfg["width"]), int(cfg["vocab"]), int(context_length), float(cfg["norm"]["eps"]), 1.0, layers, None,
+        block="outnorm", norm_groups=int(cfg["norm"].get("groups", 1)), token_shift=True, depth_average=True)
+
+
 # config.json "architecture" -> (model type, configuration builder): the registry of safetensors model directories
 CONFIG_ARCHITECTURES = {"Pibidra": ("PIBIDRA", pibidra_configuration), "Latusun": ("LATUSUN", latusun_configuration),
-                        "Lerosun": ("LEROSUN", lerosun_configuration)}
+                        "Lerosun": ("LEROSUN", lerosun_configuration), "Dinuzen": ("DINUZEN", dinuzen_configuration)}
 DEFAULT_LAYERED_CONTEXT = 4096
 
 

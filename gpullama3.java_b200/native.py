@@ -40,22 +40,27 @@ class LayerSpec(C.Structure):
                [(n, C.c_int32) for n in ("sink", "gate", "qkv_bias", "qk_norm", "ff_kind", "ff_dim", "ff_act")] + \
                [(n, C.c_int32) for n in ("rot_dim", "kv_rank", "kv_from", "rope_dims", "rope_layout")] + \
                [(n, C.c_float) for n in ("rope_base", "yarn_factor", "yarn_original", "yarn_fast", "yarn_slow")] + \
-               [(n, C.c_int32) for n in ("ff_experts", "ff_top", "value_from_key", "head_temp", "head_mix", "conv_taps")]
+               [(n, C.c_int32) for n in ("ff_experts", "ff_top", "value_from_key", "head_temp", "head_mix", "conv_taps", "score_maps")] + \
+               [("diff_init", C.c_float)] + \
+               [(n, C.c_int32) for n in ("qk_head_norm", "mixer_norm_groups", "moe_router", "moe_identity")] + \
+               [("moe_scale", C.c_float), ("moe_shared_ff", C.c_int32)]
 
 
 class LayeredConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("arch", "width", "vocab_size", "n_layers", "context_length")] + \
                [("norm_eps", C.c_float), ("embedding_scale", C.c_float)] + \
                [(n, C.c_int32) for n in ("loop_start", "loop_stop", "loop_times", "compute", "block")] + \
-               [("residual_mult", C.c_float), ("logit_softcap", C.c_float)]
+               [("residual_mult", C.c_float), ("logit_softcap", C.c_float)] + \
+               [(n, C.c_int32) for n in ("norm_groups", "token_shift", "depth_average")]
 
 
 COMPUTE_BF16, COMPUTE_F32 = 0, 1
-ACTIVATIONS = {"gelu_tanh": 0, "silu": 1, "relu": 2}
-MIXERS = {"window_attention": 1, "latent_attention": 2, "gated_delta": 3}
-FF_KINDS = {"none": 0, "dense": 1, "moe": 2}
+ACTIVATIONS = {"gelu_tanh": 0, "silu": 1, "relu": 2, "gelu_erf": 3}
+MIXERS = {"window_attention": 1, "latent_attention": 2, "gated_delta": 3, "rglru": 4, "ssd": 5}
+FF_KINDS = {"none": 0, "dense": 1, "moe": 2, "dense_plain": 3}
+MOE_ROUTERS = {"sigmoid_input": 0, "softmax_output": 1}
 ROPE_LAYOUTS = {"half": 0, "interleaved": 1}
-BLOCKS = {"sandwich": 0, "parallel": 1, "prenorm": 2}
+BLOCKS = {"sandwich": 0, "parallel": 1, "prenorm": 2, "outnorm": 3}
 
 
 class Tensor(C.Structure):

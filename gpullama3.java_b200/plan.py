@@ -66,6 +66,7 @@ def make_layered_config(model: Model, compute: str = "bfloat16"):
     cfg.loop_start, cfg.loop_stop, cfg.loop_times = c.loop if c.loop is not None else (0, 0, -1)
     cfg.compute = {"bfloat16": native.COMPUTE_BF16, "bf16": native.COMPUTE_BF16, "float32": native.COMPUTE_F32, "f32": native.COMPUTE_F32}[compute]
     cfg.block, cfg.residual_mult, cfg.logit_softcap = native.BLOCKS[c.block], c.residual_mult, c.logit_softcap
+    cfg.norm_groups, cfg.token_shift, cfg.depth_average = c.norm_groups, int(c.token_shift), int(c.depth_average)
     specs = []
     for s in c.layers:
         if s.mixer not in native.MIXERS:
@@ -84,6 +85,8 @@ def make_layered_config(model: Model, compute: str = "bfloat16"):
         sp.rot_dim, sp.kv_rank, sp.kv_from = s.rot_dim, s.kv_rank, s.kv_from
         sp.rope_dims, sp.rope_layout, sp.rope_base = s.rope_dims, native.ROPE_LAYOUTS[s.rope_layout], s.rope_base
         sp.yarn_factor, sp.yarn_original, sp.yarn_fast, sp.yarn_slow = s.yarn
+        sp.score_maps, sp.diff_init, sp.qk_head_norm, sp.mixer_norm_groups = s.score_maps, s.diff_init, int(s.qk_head_norm), s.mixer_norm_groups
+        sp.moe_router, sp.moe_identity, sp.moe_scale, sp.moe_shared_ff = native.MOE_ROUTERS[s.moe_router], s.moe_identity, s.moe_scale, s.moe_shared_ff
         specs.append(sp)
     return cfg, specs
 

@@ -56,6 +56,13 @@ extern "C" {
                              * sink logit per head, one sigmoid gate per head) or a gated delta rule (a recurrent state matrix per head behind
                              * short causal convolutions); a gated ReLU feed-forward; a block of layers may run several passes */
 
+#define B200_ARCH_DINUZEN 6 /* a layered design: x += s1 * GN(mixer(shift x)); x += s2 * GN(ff(x)) with the norm (RMS in groups) on the sublayer's OUTPUT
+                             * only, a token shift in front of every mixer, and the depth average x <- sum_j dwa[j] X_j over the results of all
+                             * earlier layers behind every layer; the mixer is a real-gated linear recurrent unit, a state-space recurrence
+                             * with a matrix state per head, or a differential attention (two softmax maps per head over the same values,
+                             * subtracted), which may read another layer's keys and values; the feed-forward is a plain GELU layer or a
+                             * softmax-routed mixture of gated SiLU experts with identity experts and a gated shared expert */
+
 /* GGML tensor type ids accepted for weights (tensor/GGMLType.java:5-20) */
 #define B200_GGML_F32 0
 #define B200_GGML_F16 1
@@ -128,20 +135,41 @@ int b200_plan_create(const b200_config *cfg, const b200_tensor *tensors, int32_t
                                   * softplus(W_a a + dt_bias)) per head; per head S <- gamma S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q;
                                   * y = o / rms(o) * w ("<layer>.mix.norm" [value_dim]) * silu(W_g a); W_o.  The state S [key_dim][value_dim] per
                                   * head (FP32, zero at position 0) and the last conv_taps - 1 convolution inputs are carried between calls */
+#define B200_MIXER_RGLRU 4 /* two branches of value_dim * heads channels ("<layer>.mix.y", ".x" with biases ".y.b", ".x.b"): y = gelu_tanh(Wy a + by),
+                            * u = conv(Wx a + bx) + bc (causal, conv_taps taps per channel, ".conv" [channels][taps], ".conv.b", no activation); per
+                            * diagonal block b of `heads` blocks r = sigmoid(Ra[b] u_b + ra_b[b]), i = sigmoid(Ri[b] u_b + ri_b[b]) (".ra" / ".ri"
+                            * [blocks][out][in], ".ra.b" / ".ri.b"); a = exp(-8 r softplus(lam)) (".lam"); S <- a S + sqrt(1 - a^2) i u from S = 0;
+                            * W_o (S * y).  S (FP32) and the last conv_taps - 1 convolution inputs are carried between calls */
+#define B200_MIXER_SSD 5   /* W_in a = [z: heads * value_dim | x: heads * value_dim | B: kv_heads * key_dim | C: kv_heads * key_dim | dt: heads] (".in");
+                            * [x | B | C] pass a causal convolution (".conv", ".conv.b") and SiLU; dt = softplus(dt + dt_bias); per head (group
+                            * h / (heads / kv_heads)) a state S [key_dim][value_dim]: S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x;
+                            * y * silu(z) is RMS-normed in mixer_norm_groups parts times ".norm", then W_o.  S (FP32) and the last conv_taps - 1
+                            * convolution inputs are carried between calls */
 #define B200_FF_NONE 0
 #define B200_FF_DENSE_GATED 1 /* down(act(gate x) * (up x)) */
 #define B200_FF_MOE 2         /* sum over the ff_top experts with the largest router scores of expert_e(s_e * x), expert = FF_DENSE_GATED without
                                * biases ("<layer>.mlp.e<k>.{gate,up,down}"), s = sigmoid(Wrouter x) in FP32, not renormalised */
+#define B200_FF_DENSE_PLAIN 3 /* down(act(up x)) ("<layer>.mlp.{up,down}") */
+#define B200_MOE_SIGMOID_INPUT 0 /* s = sigmoid(z); the `top` largest; the score scales what the expert READS; no renormalisation */
+#define B200_MOE_SOFTMAX_OUTPUT 1 /* s = softmax(z) over experts + identity experts; the `top` largest of s + "<layer>.mlp.correction" are chosen;
+                                   * weights s / (sum of the chosen s + 1e-20) * moe_scale multiply the experts' OUTPUTS; the last moe_identity router
+                                   * outputs are identity experts (output = input, no tensors) */
 #define B200_ROPE_HALF 0        /* pair (i, i + rot_dims / 2) */
 #define B200_ROPE_INTERLEAVED 1 /* pair (2i, 2i + 1) */
 #define B200_BLOCK_SANDWICH 0 /* x += N(mixer(N x)); x += N(ff(N x)) with (1 + w)-weighted RMS norms (Pibidra) */
 #define B200_BLOCK_PRENORM 2  /* x += s1 * mixer(R(x; g1)); x += s2 * ff(R(x; g2)): R = RMS norm times ONE number ("<layer>.norm1", a scalar tensor),
                                * s = a vector ("<layer>.ls1"); the embedding output passes R(.; "embed.norm"); a loop block repeats without a
                                * prologue (nothing is re-added between passes) */
+#define B200_BLOCK_OUTNORM 3  /* x += s1 * GN(mixer(h); w1); x += s2 * GN(ff(x); w2): the sublayers read x itself, the norm (RMS norm in norm_groups equal
+                               * consecutive parts, weights used as stored, "<layer>.norm1" / ".norm2") sits on the sublayer's output, s = "<layer>.ls1" /
+                               * ".ls2".  token_shift: h[t] = x[t] + (x[t-1] - x[t]) * "<layer>.shift" (x[-1] = 0; the previous row is part of the
+                               * sequence's state in every layer); depth_average: behind layer i, x <- sum_{j <= i+1} "<layer>.dwa"[j] X_j with X_0
+                               * the embedding output and X_(i+1) layer i's result before the averaging.  The final norm is the grouped one too */
 #define B200_BLOCK_PARALLEL 1 /* x += residual_mult * (mixer(LN1 x) + ff(LN2 x)), layer norms with weight and bias ("<layer>.norm1", ".norm1.b", ...) */
 #define B200_ACT_GELU_TANH 0
 #define B200_ACT_SILU 1
 #define B200_ACT_RELU 2
+#define B200_ACT_GELU_ERF 3
 #define B200_COMPUTE_BF16 0 /* prefill GEMM operands rounded to BF16, FP32 accumulation; decode FP32 activations x BF16 weights */
 #define B200_COMPUTE_F32 1  /* every product in true FP32 (BF16 weights widen exactly) */
 
@@ -185,10 +213,26 @@ typedef struct b200_layer_spec {
     int32_t head_mix;       /* 1: score_h <- sum_m T[h][m] score_m over the query heads before cap, bias and softmax ("<layer>.mix.talk" [heads][heads]) */
     /* B200_MIXER_GATED_DELTA */
     int32_t conv_taps;      /* taps of the causal convolution (>= 1) */
+    /* B200_MIXER_WINDOW_ATTENTION in a B200_BLOCK_OUTNORM plan */
+    int32_t score_maps;     /* 2: differential attention.  q has heads * 2 * key_dim rows and k kv_heads * 2 * key_dim, head by head as [map 1 | map 2];
+                               each map is a softmax attention of its own over the same values, o = a1 - lambda a2 with lambda =
+                               exp(<lq1, lk1>) - exp(<lq2, lk2>) + diff_init ("<layer>.mix.lq1" ... [key_dim]), then o / rms(o) over the head's values
+                               (no weight) times (1 - diff_init).  0 / 1: one map */
+    float diff_init;
+    int32_t qk_head_norm;   /* 1: every key_dim slice of q and k (per head and map) is RMS-normed with ONE weight of size key_dim
+                               ("<layer>.mix.q.norm" / ".k.norm"), before the rotation */
+    /* B200_MIXER_SSD */
+    int32_t mixer_norm_groups; /* parts of the read-out's RMS norm */
+    /* B200_FF_MOE */
+    int32_t moe_router;     /* B200_MOE_* */
+    int32_t moe_identity;   /* identity experts behind the ff_experts real ones */
+    float moe_scale;
+    int32_t moe_shared_ff;  /* > 0: a shared expert of that width ("<layer>.mlp.shared.{gate,up,down}") runs for every token and is added times
+                               sigmoid(<"<layer>.mlp.shared.sg", x>) */
 } b200_layer_spec;
 
 typedef struct b200_layered_config {
-    int32_t arch;           /* B200_ARCH_PIBIDRA, B200_ARCH_LATUSUN, B200_ARCH_LEROSUN */
+    int32_t arch;           /* B200_ARCH_PIBIDRA, B200_ARCH_LATUSUN, B200_ARCH_LEROSUN, B200_ARCH_DINUZEN */
     int32_t width;
     int32_t vocab_size;
     int32_t n_layers;
@@ -200,6 +244,9 @@ typedef struct b200_layered_config {
     int32_t block;          /* B200_BLOCK_* */
     float residual_mult;    /* B200_BLOCK_PARALLEL: multiplies what a layer adds to the residual */
     float logit_softcap;    /* > 0: logits <- cap * tanh(logits / cap) */
+    int32_t norm_groups;    /* B200_BLOCK_OUTNORM: parts of every residual norm (>= 1; 0 reads as 1) */
+    int32_t token_shift;    /* B200_BLOCK_OUTNORM: 1 = the mixers read the shifted row */
+    int32_t depth_average;  /* B200_BLOCK_OUTNORM: 1 = the depth average behind every layer */
 } b200_layered_config;
 
 /* prefill_batch_size = the most tokens one b200_forward_batch_prefill / _batch_logits call takes (>= 1). */
