@@ -625,3 +625,117 @@ def lerosun_model(cfg: dict, weights: dict, context_length: int):
 
 
 write_model_dir = write_pibidra_dir  # config.json + model.safetensors of any layered design
+
+
+# ---- Dinuzen: blocks with the norm on the sublayer's output, token shift, depth average -----------------------------------------
+def dinuzen_attention(heads: int, kv_heads: int, key_dim: int, value_dim: int, mlp: dict | None = None, *, rot_dims: int | None = None, base: float = 10000.0,
+                      scaling: tuple | None = None, scale: float | None = None, softcap: float = 30.0, diff: float = 0.3, kv_from: int | None = None) -> dict:
+    """A differential-attention entry of config.json's "layers" (scaling = (factor, original, fast, slow) or None)."""
+    rot = {"dims": key_dim // 2 * 2 if rot_dims is None else rot_dims, "base": float(base)}
+    if scaling is not None:
+        rot["scaling"] = {"factor": float(scaling[0]), "original": scaling[1], "fast": float(scaling[2]), "slow": float(scaling[3])}
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": key_dim, "vdim": value_dim, "rot": rot, "scale": float(key_dim ** -0.5 if scale is None else scale),
+         "softcap": float(softcap), "diff": float(diff)}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return {"type": "attention", "mixer": m, "mlp": mlp}
+
+
+def dinuzen_rglru(width: int, blocks: int, taps: int, mlp: dict | None = None) -> dict:
+    return {"type": "rglru", "mixer": {"width": width, "blocks": blocks, "conv": taps}, "mlp": mlp}
+
+
+def dinuzen_mamba2(heads: int, value_dim: int, state: int, groups: int, taps: int, mlp: dict | None = None, norm_groups: int = 1) -> dict:
+    return {"type": "mamba2", "mixer": {"heads": heads, "vdim": value_dim, "state": state, "groups": groups, "conv": taps, "norm_groups": norm_groups}, "mlp": mlp}
+
+
+def dinuzen_dense(ff: int) -> dict:
+    return {"kind": "dense", "ff": ff}
+
+
+def dinuzen_moe(experts: int, top: int, ff: int, identity: int = 0, scale: float = 1.0, shared: int | None = None) -> dict:
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "identity": identity, "top": top, "scale": float(scale)},
+            "shared": None if shared is None else {"ff": shared}}
+
+
+def dinuzen_config(width: int, vocab: int, layers: list, eps: float = 1e-5, groups: int = 1) -> dict:
+    return {"architecture": "Dinuzen", "width": width, "vocab": vocab, "norm": {"eps": float(eps), "groups": groups}, "layers": layers}
+
+
+def dinuzen_weights(cfg: dict, seed: int = 0) -> dict:
+    """name -> float32 array in the shapes the loader expects (linear weights [out][in]); BF16-representable values."""
+    from .safetensors import bf16_bits, bf16_to_f32
+
+    rng = np.random.default_rng(seed)
+    E, V = cfg["width"], cfg["vocab"]
+    w = {}
+
+    def mat(o, i, gain=1.0):
+        return (rng.standard_normal((o, i)) * gain / np.sqrt(i)).astype(np.float32)
+
+    def vec(n, mean=0.0, std=1.0):
+        return (mean + std * rng.standard_normal(n)).astype(np.float32)
+
+    w["embed"] = rng.standard_normal((V, E)).astype(np.float32)
+    w["final.norm"] = vec(E, 1.0, 0.2)
+    w["head"] = mat(V, E)
+    for i, lc in enumerate(cfg["layers"]):
+        m, p = lc["mixer"], f"l{i}."
+        w[p + "norm1"], w[p + "ls1"] = vec(E, 1.0, 0.2), vec(E, 0.5, 0.2)
+        w[p + "shift"] = rng.uniform(0.0, 1.0, E).astype(np.float32)
+        dwa = 0.15 * rng.standard_normal(i + 2)
+        dwa[-1] += 1.0
+        w[p + "dwa"] = dwa.astype(np.float32)
+        if lc["type"] == "attention":
+            H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            w[p + "mix.q"], w[p + "mix.q.norm"] = mat(H * 2 * dk, E, 1.5), vec(dk, 1.0, 0.3)
+            if m.get("kv_from") is None:
+                w[p + "mix.k"], w[p + "mix.v"], w[p + "mix.k.norm"] = mat(G * 2 * dk, E, 1.5), mat(G * dv, E), vec(dk, 1.0, 0.3)
+            for n in ("lq1", "lk1", "lq2", "lk2"):
+                w[p + "mix." + n] = vec(dk, 0.0, 0.5 / np.sqrt(dk) ** 0.5)
+            w[p + "mix.o"] = mat(E, H * dv)
+        elif lc["type"] == "rglru":
+            W, nb, K = m["width"], m["blocks"], m["conv"]
+            bs = W // nb
+            w[p + "mix.x"], w[p + "mix.x.b"] = mat(W, E), vec(W, 0.0, 0.2)
+            w[p + "mix.y"], w[p + "mix.y.b"] = mat(W, E), vec(W, 0.0, 0.2)
+            w[p + "mix.conv"], w[p + "mix.conv.b"] = (rng.standard_normal((W, K)) * 0.6).astype(np.float32), vec(W, 0.0, 0.2)
+            w[p + "mix.ra"], w[p + "mix.ra.b"] = (rng.standard_normal((nb, bs, bs)) / np.sqrt(bs)).astype(np.float32), vec(W, 0.0, 0.5).reshape(nb, bs)
+            w[p + "mix.ri"], w[p + "mix.ri.b"] = (rng.standard_normal((nb, bs, bs)) / np.sqrt(bs)).astype(np.float32), vec(W, 0.0, 0.5).reshape(nb, bs)
+            w[p + "mix.lam"] = vec(W, -2.0, 1.0)
+            w[p + "mix.o"] = mat(E, W)
+        else:
+            H, P, N, G, K = m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
+            inner, C = H * P, H * P + 2 * G * N
+            w[p + "mix.in"] = mat(2 * inner + 2 * G * N + H, E)
+            w[p + "mix.conv"], w[p + "mix.conv.b"] = (rng.standard_normal((C, K)) * 0.6).astype(np.float32), vec(C, 0.0, 0.2)
+            w[p + "mix.dt_bias"], w[p + "mix.A_log"], w[p + "mix.D"] = vec(H, -1.0, 0.7), vec(H, -0.5, 0.7), vec(H, 1.0, 0.3)
+            w[p + "mix.norm"] = vec(inner, 1.0, 0.2)
+            w[p + "mix.o"] = mat(E, inner)
+        mlp = lc.get("mlp")
+        if mlp is None:
+            continue
+        w[p + "norm2"], w[p + "ls2"] = vec(E, 1.0, 0.2), vec(E, 0.5, 0.2)
+        if mlp["kind"] == "dense":
+            w[p + "mlp.up"], w[p + "mlp.down"] = mat(mlp["ff"], E), mat(E, mlp["ff"])
+            continue
+        r, F = mlp["router"], mlp["expert"]["ff"]
+        XI = r["experts"] + r.get("identity", 0)
+        w[p + "mlp.router"], w[p + "mlp.correction"] = mat(XI, E, 1.5), vec(XI, 0.0, 0.05)
+        for e in range(r["experts"]):
+            w[p + f"mlp.e{e}.gate"], w[p + f"mlp.e{e}.up"], w[p + f"mlp.e{e}.down"] = mat(F, E), mat(F, E), mat(E, F)
+        if mlp.get("shared"):
+            SF = mlp["shared"]["ff"]
+            w[p + "mlp.shared.gate"], w[p + "mlp.shared.up"], w[p + "mlp.shared.down"] = mat(SF, E), mat(SF, E), mat(E, SF)
+            w[p + "mlp.shared.sg"] = mat(1, E, 2.0)
+    return {k: bf16_to_f32(bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
+
+
+def dinuzen_model(cfg: dict, weights: dict, context_length: int):
+    """In-memory loader.Model (benchmarks and tests: synthetic weights never touch the disk)."""
+    from . import loader
+    from .safetensors import bf16_bits
+
+    tensors = {k: (loader.GGML_BF16, tuple(reversed(v.shape)), bf16_bits(v).view(np.uint8).reshape(-1)) for k, v in weights.items()}
+    config = loader.dinuzen_configuration(cfg, {k: v.shape for k, v in weights.items()}, context_length)
+    return loader.Model(None, config, "DINUZEN", tensors)

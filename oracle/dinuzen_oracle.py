@@ -196,7 +196,9 @@ def mixer_attention(h, w: dict, pre: str, m: dict, eps: float, kv):
         g = hd // (H // G)
         maps = []
         for mp in range(2):
-            e = softcap((q[:, hd, mp] @ k[:, g, mp].T) * float(m["scale"]), float(m["softcap"]))
+            e = (q[:, hd, mp] @ k[:, g, mp].T) * float(m["scale"])
+            if m.get("softcap"):
+                e = softcap(e, float(m["softcap"]))
             e = np.where(np.tril(np.ones((T, T), dtype=bool)), e, -np.inf)
             p = np.exp(e - e.max(-1, keepdims=True))
             p /= p.sum(-1, keepdims=True)
@@ -216,7 +218,7 @@ def rglru_gates(u, w: dict, pre: str, blocks: int):
 
 
 def rglru_scan(u, r, i, lam):
-    """S[t] = a S[t-1] + sqrt(1 - a^2) (i u) with a = exp(-8 r softplus(lam)), from S = 0 (the first token is no special case)."""
+    """S[t] = a S[t-1] + sqrt(1 - a^2) (i u) with a = exp(-8 r softplus(lam)), from S = 0; token 0 runs the same update as every other."""
     T, W = u.shape
     a = np.exp(-8.0 * r * softplus(lam))
     S = np.zeros(W)
@@ -301,8 +303,9 @@ def ff_moe(x, w: dict, pre: str, mlp: dict):
 
 
 # ---- model -------------------------------------------------------------------------------------------------------------
-def forward(cfg: dict, w: dict, tokens, return_layers: bool = False):
-    """Logits [T, vocab] of the whole sequence (and, optionally, the residual stream after every layer [layers, T, E])."""
+def forward(cfg: dict, w: dict, tokens, return_layers: bool = False, on_moe_input=None):
+    """Logits [T, vocab] of the whole sequence (and, optionally, the residual stream after every layer [layers, T, E]).
+    on_moe_input(layer, x) is called with what every mixture of experts reads."""
     eps, groups = float(cfg["norm"]["eps"]), int(cfg["norm"]["groups"])
     x = w["embed"][np.asarray(tokens)]
     streams = [x]
@@ -324,6 +327,8 @@ def forward(cfg: dict, w: dict, tokens, return_layers: bool = False):
         x = x + w[pre + "ls1"] * group_rms_norm(y, w[pre + "norm1"], groups, eps)
         mlp = lc.get("mlp")
         if mlp is not None:
+            if on_moe_input is not None and mlp["kind"] == "moe":
+                on_moe_input(i, x)
             y = ff_dense(x, w, pre + "mlp.") if mlp["kind"] == "dense" else ff_moe(x, w, pre + "mlp.", mlp)
             x = x + w[pre + "ls2"] * group_rms_norm(y, w[pre + "norm2"], groups, eps)
         streams.append(x)
