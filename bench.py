@@ -316,6 +316,82 @@ def compare_lerosun(pkg, lb, local: int, steps: int, warmup: int, sizes):
             "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "tensor_tflops": burst, "tensor_source": t_src}, "sizes": out}
 
 
+# ---- --compare dinuzen: the output-normed hybrid (differential attention, real-gated recurrent unit, state-space recurrence,
+# softmax-routed experts) beside the closest existing model (Lerosun: the other hybrid of attention and a recurrence with a short
+# convolution) -----
+# Both are layered plans with BF16 weights, an FP32 residual, key rings, recurrent states with convolution rings and the same
+# projection kernels.  Equal size = same width, vocabulary, number of layers and layer order (recurrent, attention, recurrent,
+# attention), the same number of score maps per token (Dinuzen: heads x 2 maps; Lerosun: 2 x heads), the same key size, and a dense
+# feed-forward as wide as what one Dinuzen token uses (chosen experts + shared expert).
+DINUZEN_SIZES = {
+    # name: (width, attention heads, key/value heads, key = value size per map, recurrent-unit blocks, state-space heads, value size, state size, taps,
+    #        experts, identity experts, chosen, expert ff, shared ff, dense ff, vocab, Lerosun delta (value heads, q/k heads, key size, value size))
+    "small": (1024, 8, 2, 64, 8, 32, 64, 128, 4, 8, 1, 2, 1024, 1024, 4096, 32768, (8, 4, 64, 128)),
+    "1b-like": (2048, 8, 2, 128, 16, 64, 64, 128, 4, 16, 2, 4, 1408, 2816, 8192, 32768, (16, 8, 128, 128)),
+}
+
+
+def dinuzen_compare_models(S, name: str, ctx: int):
+    """(Dinuzen config, Lerosun config, accounting) of one compare size."""
+    E, H, G, dk, nb, SH, SP, SN, taps, X, I, top, F, SF, DF, V, (DH, DG, ddk, ddv) = DINUZEN_SIZES[name]
+    moe = S.dinuzen_moe(X, top, F, identity=I, scale=2.0, shared=SF)
+    layers = [S.dinuzen_mamba2(SH, SP, SN, 1, taps, moe), S.dinuzen_attention(H, G, dk, dk, S.dinuzen_dense(DF), scaling=(4.0, 4096, 32.0, 1.0)),
+              S.dinuzen_rglru(E, nb, taps, moe), S.dinuzen_attention(H, G, dk, dk, moe, scaling=(4.0, 4096, 32.0, 1.0), kv_from=1)]
+    cfg = S.dinuzen_config(E, V, layers, groups=4)
+    real = top * X / (X + I)  # experts a token streams on average when every expert is equally likely
+    moe_w = (X + I + 1) * E + 3 * SF * E + real * 3 * F * E
+    inner = SH * SP
+    w_ssd = (2 * inner + 2 * SN + SH) * E + inner * E + moe_w
+    w_att = (H * 2 * dk + G * 2 * dk + G * dk) * E + H * dk * E + 2 * DF * E
+    w_rg = 2 * E * E + 2 * E * (E // nb) + E * E + moe_w
+    w_att2 = H * 2 * dk * E + H * dk * E + moe_w
+    streamed = w_ssd + w_att + w_rg + w_att2
+    FL = top * F + SF  # the closest model's dense feed-forward: as wide as what one token uses here
+    att, dlt = S.lerosun_attention(2 * H, G, dk, ctx, FL, rot_dims=dk // 2), S.lerosun_delta(DH, DG, ddk, ddv, taps, FL)
+    lcfg = S.lerosun_config(E, V, [dlt, att, dlt, att])
+    l_att = (2 * H * dk + G * dk + 2 * H) * E + 2 * H * dk * E + 3 * FL * E
+    l_dlt = (2 * DG * ddk + 2 * DH * ddv + 2 * DH) * E + DH * ddv * E + 3 * FL * E
+    acct = {"streamed": streamed, "ssd_mac_per_token": 3 * SH * SN * SP, "att_mac_per_pair": H * 2 * (dk + dk), "l_streamed": 2 * (l_att + l_dlt),
+            "l_att_mac_per_pair": 2 * H * 2 * dk, "l_delta_mac_per_token": 3 * DH * ddk * ddv}
+    return cfg, lcfg, acct
+
+
+def compare_dinuzen(pkg, lb, local: int, steps: int, warmup: int, sizes):
+    hbm, hbm_src = peaks()
+    burst, sustained, t_src = tensor_peak()
+    S = pkg.synth
+    out = {}
+    for name in sizes:
+        E, V = DINUZEN_SIZES[name][0], DINUZEN_SIZES[name][15]
+        depth, n_pp = 64, 512
+        ctx = max(depth + steps + warmup + 8, n_pp + 8)
+        toks = np.asarray(lb.synthetic_tokens(V, ctx), dtype=np.int32)
+        cfg, lcfg, a = dinuzen_compare_models(S, name, ctx)
+        pairs = n_pp * (n_pp + 1) // 2
+        w = S.dinuzen_weights(cfg, 1234)
+        plan = pkg.B200MasterPlan.initialize_plan(S.dinuzen_model(cfg, w, ctx), prefill_batch_size=n_pp, device=local, compute="bfloat16")
+        row = {"dinuzen_bfloat16": _layered_leg(plan, toks, depth, warmup, steps, n_pp, hbm, burst, 2 * (a["streamed"] + V * E),
+                                                2.0 * a["streamed"] * n_pp + 2.0 * (2 * a["att_mac_per_pair"] * pairs + a["ssd_mac_per_token"] * n_pp),
+                                                ((0, "up_or_gate_up"), (1, "down"), (2, "fused_projection"), (3, "mixer_out"), (4, "classifier")))}
+        plan.free()
+        del w
+        lw = S.lerosun_weights(lcfg, 1234)
+        plan = pkg.B200MasterPlan.initialize_plan(S.lerosun_model(lcfg, lw, ctx), prefill_batch_size=n_pp, device=local, compute="bfloat16")
+        row["lerosun_bfloat16"] = _layered_leg(plan, toks, depth, warmup, steps, n_pp, hbm, burst, 2 * (a["l_streamed"] + V * E),
+                                               2.0 * a["l_streamed"] * n_pp + 2.0 * (2 * a["l_att_mac_per_pair"] * pairs + 2 * a["l_delta_mac_per_token"] * n_pp),
+                                               ((0, "gate_up"), (1, "down"), (2, "fused_projection"), (3, "mixer_out"), (4, "classifier")))
+        plan.free()
+        del lw
+        row["config"] = {"width": E, "vocab": V, "layers": 4, "order": "state space, attention, recurrent unit, attention reading the first one's keys",
+                         "sizes": dict(zip(("width", "attention_heads", "kv_heads", "key_value_size_per_map", "unit_blocks", "ssd_heads", "ssd_value", "ssd_state", "taps", "experts",
+                                            "identity_experts", "chosen", "expert_ff", "shared_ff", "dense_ff", "vocab"), DINUZEN_SIZES[name][:16])),
+                         "closest": "Lerosun: delta, attention, delta, attention with twice the heads of the same key size and a dense feed-forward of chosen x expert ff + shared ff",
+                         "decode": f"tg{steps} from depth {depth + warmup}", "prefill": f"pp{n_pp} in one chunk from depth 0"}
+        out[name] = row
+    return {"metric": "dinuzen_vs_closest_model", "unit": "tok/s", "data": "synthetic", "dtype": "bf16 weights, f32 accumulate",
+            "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "tensor_tflops": burst, "tensor_source": t_src}, "sizes": out}
+
+
 class ClockSampler:
     """nvidia-smi clocks/throttle reasons sampled DURING the timed region."""
     Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
@@ -431,10 +507,10 @@ def main():
     ap.add_argument("--depth", type=int, default=-1, help="LlamaBench -d: KV positions filled before the timed steps (default: the warm-up steps)")
     ap.add_argument("--workload", default=WORKLOAD, choices=["llama-3-8b", "llama-3-70b", "llama-3.2-1b", "qwen3-4b"],
                     help="shape of the synthetic model (default: the BASELINE headline, Llama-3-8B; 70B is BASELINE config 5, meant for --gpus 2/4/8)")
-    ap.add_argument("--compare", default=None, choices=["pibidra", "latusun", "lerosun"],
+    ap.add_argument("--compare", default=None, choices=["pibidra", "latusun", "lerosun", "dinuzen"],
                     help="instead of the headline workload: decode and prefill throughput of a layered design beside its closest existing model "
-                         "at equal sizes (pibidra: the FP16 Qwen3 plan; latusun, lerosun: the Pibidra plan), with per-kernel rooflines; one JSON line")
-    ap.add_argument("--compare-sizes", default=None, help="comma-separated size names (pibidra: 1b-like,8b-like; latusun: small,lite-like; lerosun: small,1b-like)")
+                         "at equal sizes (pibidra: the FP16 Qwen3 plan; latusun, lerosun: the Pibidra plan; dinuzen: the Lerosun plan), with per-kernel rooflines; one JSON line")
+    ap.add_argument("--compare-sizes", default=None, help="comma-separated size names (pibidra: 1b-like,8b-like; latusun: small,lite-like; lerosun, dinuzen: small,1b-like)")
     args = ap.parse_args()
     K, W = args.steps, max(args.warmup, 3)
     if args.compare:
@@ -445,7 +521,9 @@ def main():
         pkg = ge.import_package()
         sampler = ClockSampler(local)
         sampler.start()
-        if args.compare == "lerosun":
+        if args.compare == "dinuzen":
+            line = compare_dinuzen(pkg, pkg.llama_bench, local, min(K, 64), W, (args.compare_sizes or "small,1b-like").split(","))
+        elif args.compare == "lerosun":
             line = compare_lerosun(pkg, pkg.llama_bench, local, min(K, 64), W, (args.compare_sizes or "small,1b-like").split(","))
         elif args.compare == "latusun":
             line = compare_latusun(pkg, pkg.llama_bench, local, min(K, 64), W, (args.compare_sizes or "small,lite-like").split(","))

@@ -627,7 +627,8 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             CK(set_max_dyn(ly::k_delta_prep, Y.smem_max));
             CK(set_max_dyn(ly::k_rope_mix_prep, Y.smem_max));
             CK(set_max_dyn(ly::k_delta_rule, Y.smem_max));
-            CK(set_max_dyn(ly::k_outnorm_rows, Y.smem_max));
+            CK(set_max_dyn(ly::k_outnorm_rows<LY_NORM_THREADS>, Y.smem_max));
+            CK(set_max_dyn(ly::k_outnorm_rows<1024>, Y.smem_max));
             CK(set_max_dyn(ly::k_gated_group_norm, Y.smem_max));
             CK(set_max_dyn(ly::k_matvec_bf16<ly::EPI_ACT>, Y.smem_max));
             attrs = true;
@@ -966,7 +967,7 @@ static int ly_batch(b200_plan *p, const int32_t *tokens, int n, int start_pos, c
             ly::OutNormArgs a = ly_outnorm_args(Y, m);
             a.w_out = Y.final_norm; a.gather = Y.rows; a.st = Y.st_pf;
             a.out32 = Y.f32 ? Y.A32 : nullptr; a.out16 = Y.f32 ? nullptr : Y.A16;
-            if ((rc = launch_k(p, false, ly::k_outnorm_rows, dim3(m), dim3(LY_NORM_THREADS), (size_t)2 * E * 4, a))) return rc;
+            if ((rc = launch_k(p, false, ly::k_outnorm_rows<LY_NORM_THREADS>, dim3(m), dim3(LY_NORM_THREADS), (size_t)2 * E * 4, a))) return rc;
         } else if (Y.c.block == B200_BLOCK_PARALLEL) {
             ly::BlockNormArgs a = ly_block_norm_args(Y);
             a.w1 = Y.final_norm; a.b1 = Y.final_norm_b; a.gather = Y.rows;

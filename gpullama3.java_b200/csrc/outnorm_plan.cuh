@@ -300,7 +300,9 @@ static int ly_enqueue_outnorm(b200_plan *p, bool decode, int n, const StepState 
         if (out) { a.out32 = h16 ? nullptr : Y.A32; a.out16 = h16 ? Y.A16 : nullptr; }
         pend = ly_outnorm_args(Y, n);
         nl++;
-        return launch_k(p, false, ly::k_outnorm_rows, dim3(n), dim3(LY_NORM_THREADS), (size_t)2 * E * 4, a);
+        // a single row is one CTA: more threads keep more of its loads in flight
+        if (n == 1 && E >= 2048) return launch_k(p, false, ly::k_outnorm_rows<1024>, dim3(1), dim3(1024), (size_t)2 * E * 4, a);
+        return launch_k(p, false, ly::k_outnorm_rows<LY_NORM_THREADS>, dim3(n), dim3(LY_NORM_THREADS), (size_t)2 * E * 4, a);
     };
     for (size_t r = 0; r < Y.runs.size(); r++) {
         const LyRun &R = Y.runs[r];
@@ -371,8 +373,12 @@ static int ly_enqueue_outnorm(b200_plan *p, bool decode, int n, const StepState 
             }
             ly::RglruArgs ra{};
             ra.W = W; ra.blocks = nb; ra.gate_bias = L.gate_bias; ra.lam = L.lam; ra.y_bias = L.y_bias;
-            if ((rc = launch_k(p, false, ly::k_rglru_scan, dim3((W + 31) / 32), dim3(32 * RGLRU_GROUPS), (size_t)0, (const float *)Y.DLT, Y.maxD, (const float *)Y.Q, Y.maxQ,
-                               (const float *)(Y.PROJ + W), Y.maxP, ra, R.S, n, st, att32, att16, L.gd))) return rc;
+            // a chunk: 16 channels x up to 32 row groups per CTA (the last group may be short, never empty rows in between); few rows: 32 channels, one group
+            if (n >= 64) rc = launch_k(p, false, ly::k_rglru_scan<16>, dim3((W + 15) / 16), dim3(16 * RGLRU_MAX_GROUPS), (size_t)0, (const float *)Y.DLT, Y.maxD, (const float *)Y.Q, Y.maxQ,
+                                       (const float *)(Y.PROJ + W), Y.maxP, ra, R.S, n, st, att32, att16, L.gd);
+            else rc = launch_k(p, false, ly::k_rglru_scan<32>, dim3((W + 31) / 32), dim3(32), (size_t)0, (const float *)Y.DLT, Y.maxD, (const float *)Y.Q, Y.maxQ,
+                               (const float *)(Y.PROJ + W), Y.maxP, ra, R.S, n, st, att32, att16, L.gd);
+            if (rc) return rc;
             nl += 3;
         } else { // B200_MIXER_SSD
             const int inner = L.gd, gn = s.kv_heads * s.key_dim;
@@ -392,7 +398,7 @@ static int ly_enqueue_outnorm(b200_plan *p, bool decode, int n, const StepState 
             default: rc = launch_k(p, false, ly::k_ssd_scan<16>, grid, block, (size_t)0, (const float *)Y.DLT, Y.maxD, dt, Y.maxP, sa, R.S, n, st, Y.DO, Y.maxDO);
             }
             if (rc) return rc;
-            if ((rc = launch_k(p, false, ly::k_gated_group_norm, dim3(n), dim3(256), (size_t)inner * 4, (const float *)Y.DO, Y.maxDO, (const float *)Y.PROJ, Y.maxP, (const float *)L.onorm, inner,
+            if ((rc = launch_k(p, false, ly::k_gated_group_norm, dim3(n), dim3(n == 1 && inner >= 2048 ? 1024 : 256), (size_t)inner * 4, (const float *)Y.DO, Y.maxDO, (const float *)Y.PROJ, Y.maxP, (const float *)L.onorm, inner,
                                s.mixer_norm_groups, Y.c.norm_eps, att32, att16, L.gd))) return rc;
             nl += 3;
         }

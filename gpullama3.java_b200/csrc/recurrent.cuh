@@ -9,7 +9,7 @@
 //   * k_conv_rows        causal convolution per channel over a ring of its own inputs (bias on the input and on the output, optional
 //                        SiLU), any cut of the sequence into launches;
 //   * k_rglru_scan       real-gated linear recurrent unit: a = exp(-8 sigmoid(r) softplus(lam)), S <- a S + sqrt(1 - a^2) sigmoid(i) u,
-//                        output S * gelu_tanh(y): a two-level scan over the rows of a chunk;
+//                        output S * gelu_tanh(y): a two-level scan over the rows of a chunk (up to 32 row groups per CTA);
 //   * k_ssd_scan         state-space recurrence with a matrix state per head, S <- exp(-exp(A) dt) S + dt B x^T, y = S^T C + D x,
 //                        state columns in registers;
 //   * k_gated_group_norm y * silu(z), RMS norm in groups, weight;
@@ -20,6 +20,7 @@
 #pragma once
 #include "layered.cuh"
 #include "latent.cuh"
+#include "delta.cuh"
 
 namespace ly {
 
@@ -72,61 +73,88 @@ __device__ __forceinline__ void group_inv_rms(const float *v, int E, int groups,
     __syncthreads();
 }
 
-#define LY_OUTNORM_MAX_GROUPS 64
-// One CTA per row.  Dynamic shared memory: 2 * E floats.
-__global__ void __launch_bounds__(LY_NORM_THREADS) k_outnorm_rows(OutNormArgs a) {
+#define LY_OUTNORM_MAX_GROUPS 256
+#define LY_OUTNORM_SLOTS 64  // chosen experts / depth weights kept in shared memory (more: read where they are)
+// One CTA of NTH threads per row.  Dynamic shared memory: 2 * E floats.
+template <int NTH>
+__global__ void __launch_bounds__(NTH) k_outnorm_rows(OutNormArgs a) {
     extern __shared__ __align__(16) float smo[];
     __shared__ float red[32];
     __shared__ float inv[LY_OUTNORM_MAX_GROUPS];
+    __shared__ long long s_row[LY_OUTNORM_SLOTS]; // offset of a chosen expert's result row (-1: an identity expert)
+    __shared__ float s_wt[LY_OUTNORM_SLOTS], s_dwa[LY_OUTNORM_SLOTS];
     const int r = blockIdx.x, tid = threadIdx.x, E = a.E;
+    constexpr int nth = NTH;
     float *row = smo, *yv = smo + E;
     const size_t src = (size_t)(a.gather ? a.gather[r] : r) * E, dst = (size_t)r * E;
+    // the row's few indices and weights first: everything after them is independent loads
+    const bool slots = a.ys && a.top <= LY_OUTNORM_SLOTS, depth = a.stash_idx >= 0 && a.dwa && a.stash_idx < LY_OUTNORM_SLOTS;
+    if (slots && tid < a.top) {
+        const size_t e = (size_t)r * a.top + tid;
+        s_row[tid] = a.ids[e] < a.n_real ? (long long)((a.ys_map ? (size_t)a.ys_map[e] : e) * E) : -1;
+        s_wt[tid] = a.wts[e];
+    }
+    if (depth && tid <= a.stash_idx) s_dwa[tid] = a.dwa[tid];
     if (a.emb) {
         const int token = a.tokens ? a.tokens[r] : a.st->token;
         const bf16 *e = a.emb + (size_t)token * E;
-        for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] = __bfloat162float(e[i]);
+        for (int i = tid; i < E; i += nth) row[i] = __bfloat162float(e[i]);
     } else {
-        for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] = a.x[src + i];
+        for (int i = tid; i < E; i += nth) row[i] = a.x[src + i];
     }
     if (a.save_prev && r == a.n - 1)
-        for (int i = tid; i < E; i += LY_NORM_THREADS) a.save_prev[i] = row[i];
+        for (int i = tid; i < E; i += nth) a.save_prev[i] = row[i];
     const bool add = a.y || a.ys;
     if (add) {
         __syncthreads();
         if (a.ys) {
             const float sgv = a.shared ? sigmoidf_(a.sg[(size_t)r * a.sg_ld]) : 0.0f;
-            for (int i = tid; i < E; i += LY_NORM_THREADS) {
-                float s = a.shared ? sgv * a.shared[src + i] : 0.0f;
+            if (slots) { // one chosen expert per pass over the row (every thread its own entries): the loads of a pass are independent
+                for (int i = tid; i < E; i += nth) yv[i] = a.shared ? sgv * a.shared[src + i] : 0.0f;
                 for (int k = 0; k < a.top; k++) {
-                    const size_t e = (size_t)r * a.top + k;
-                    const float v = a.ids[e] < a.n_real ? a.ys[(a.ys_map ? (size_t)a.ys_map[e] : e) * E + i] : row[i];
-                    s = fmaf(a.wts[e], v, s);
+                    const float wk = s_wt[k];
+                    const float *v = s_row[k] >= 0 ? a.ys + s_row[k] : row;
+#pragma unroll 4
+                    for (int i = tid; i < E; i += nth) yv[i] = fmaf(wk, v[i], yv[i]);
                 }
-                yv[i] = s;
+            } else {
+                for (int i = tid; i < E; i += nth) {
+                    float s = a.shared ? sgv * a.shared[src + i] : 0.0f;
+                    for (int k = 0; k < a.top; k++) {
+                        const size_t e = (size_t)r * a.top + k;
+                        const float v = a.ids[e] < a.n_real ? a.ys[(a.ys_map ? (size_t)a.ys_map[e] : e) * E + i] : row[i];
+                        s = fmaf(a.wts[e], v, s);
+                    }
+                    yv[i] = s;
+                }
             }
         } else {
-            for (int i = tid; i < E; i += LY_NORM_THREADS) yv[i] = a.y[src + i];
+            for (int i = tid; i < E; i += nth) yv[i] = a.y[src + i];
         }
         __syncthreads();
         group_inv_rms(yv, E, a.groups, a.eps, inv, red);
         const int part = E / a.groups;
-        for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] = fmaf(a.ls[i], yv[i] * inv[i / part] * a.w[i], row[i]);
-    }
-    if (a.stash_idx >= 0) {
-        for (int i = tid; i < E; i += LY_NORM_THREADS) {
-            float v = row[i];
-            a.stash[(size_t)a.stash_idx * a.stash_stride + src + i] = v;
-            if (a.dwa) {
-                v *= a.dwa[a.stash_idx];
-                for (int j = 0; j < a.stash_idx; j++) v = fmaf(a.dwa[j], a.stash[(size_t)j * a.stash_stride + src + i], v);
-                row[i] = v;
+        for (int i = tid; i < E; i += nth) row[i] = fmaf(a.ls[i], yv[i] * inv[i / part] * a.w[i], row[i]);
+    } else if (depth) __syncthreads();
+    if (a.stash_idx >= 0) { // every thread touches its own entries of the row only: no barrier between the passes
+        const float *dw = depth ? s_dwa : a.dwa;
+        float *mine = a.stash + (size_t)a.stash_idx * a.stash_stride + src;
+        for (int i = tid; i < E; i += nth) mine[i] = row[i];
+        if (dw) {
+            const float wl = dw[a.stash_idx];
+            for (int i = tid; i < E; i += nth) row[i] *= wl;
+            for (int j = 0; j < a.stash_idx; j++) { // one earlier result per pass: its loads are independent of one another
+                const float wj = dw[j];
+                const float *sj = a.stash + (size_t)j * a.stash_stride + src;
+#pragma unroll 4
+                for (int i = tid; i < E; i += nth) row[i] = fmaf(wj, __ldg(sj + i), row[i]);
             }
         }
     }
     if (!a.gather && (a.emb || add || a.stash_idx >= 0))
-        for (int i = tid; i < E; i += LY_NORM_THREADS) a.x[src + i] = row[i];
+        for (int i = tid; i < E; i += nth) a.x[src + i] = row[i];
     if (a.trace)
-        for (int i = tid; i < E; i += LY_NORM_THREADS) a.trace[src + i] = row[i];
+        for (int i = tid; i < E; i += nth) a.trace[src + i] = row[i];
     if (!a.out32 && !a.out16) return;
     if (a.w_out) {
         __syncthreads();
@@ -134,7 +162,7 @@ __global__ void __launch_bounds__(LY_NORM_THREADS) k_outnorm_rows(OutNormArgs a)
     }
     const int part = E / a.groups;
     const bool first = a.shift && a.st->pos == 0;
-    for (int i = tid; i < E; i += LY_NORM_THREADS) {
+    for (int i = tid; i < E; i += nth) {
         float v = row[i];
         if (a.w_out) v = v * inv[i / part] * a.w_out[i];
         else if (a.shift) v = fmaf((first ? 0.0f : a.prev[i]) - v, a.shift[i], v);
@@ -201,9 +229,10 @@ __global__ void __launch_bounds__(256) k_conv_rows(const float *__restrict__ P, 
 //   U [n][ldu]: convolved input u;  G [n][ldg] = [block][r logits (bs) | i logits (bs)] without their biases (gate_bias has the same layout);
 //   PY [n][ldp]: the other branch before its bias and GELU.
 //   a = exp(-8 sigmoid(r) softplus(lam)),  S <- a S + sqrt(1 - a^2) sigmoid(i) u  (from S = 0 at position 0),  out = S * gelu_tanh(PY + y_bias).
-// CTA = 32 channels x RGLRU_GROUPS row groups.  A chunk of many rows is scanned on two levels: every group folds its rows into
-// (product of a, accumulated input) from a zero state, the groups' carries are chained through shared memory, then every group
-// runs its rows again from its true incoming state and writes them.  Few rows: one group, one pass.
+// CTA = CW channels x `groups` row groups (blockDim = CW * groups).  A chunk of many rows is scanned on two levels: every group
+// folds its rows into (product of a, accumulated input) from a zero state, the groups' carries are chained through shared
+// memory, then every group runs its rows again from its true incoming state and writes them; a group of at most RGLRU_KEEP rows
+// keeps its coefficients in registers between the two passes.  Few rows: one group, one pass.
 // ---------------------------------------------------------------------------------------------------------------------
 struct RglruArgs {
     int W, blocks;
@@ -211,18 +240,19 @@ struct RglruArgs {
     const float *lam;       // [W]
     const float *y_bias;    // [W]
 };
-#define RGLRU_GROUPS 8
-__global__ void __launch_bounds__(32 * RGLRU_GROUPS) k_rglru_scan(const float *__restrict__ U, int ldu, const float *__restrict__ G, int ldg, const float *__restrict__ PY, int ldp,
-                                                                   RglruArgs a, float *__restrict__ S, int n, const StepState *__restrict__ st, float *__restrict__ out32,
-                                                                   bf16 *__restrict__ out16, int ldo) {
-    __shared__ float cA[RGLRU_GROUPS][32], cB[RGLRU_GROUPS][32];
-    const int cl = threadIdx.x & 31, g = threadIdx.x >> 5, c = blockIdx.x * 32 + cl;
+#define RGLRU_MAX_GROUPS 32
+#define RGLRU_KEEP 16
+template <int CW>
+__global__ void __launch_bounds__(CW * RGLRU_MAX_GROUPS) k_rglru_scan(const float *__restrict__ U, int ldu, const float *__restrict__ G, int ldg, const float *__restrict__ PY, int ldp,
+                                                                      RglruArgs a, float *__restrict__ S, int n, const StepState *__restrict__ st, float *__restrict__ out32,
+                                                                      bf16 *__restrict__ out16, int ldo) {
+    __shared__ float cA[RGLRU_MAX_GROUPS][CW], cB[RGLRU_MAX_GROUPS][CW];
+    const int cl = threadIdx.x % CW, g = threadIdx.x / CW, c = blockIdx.x * CW + cl, groups = blockDim.x / CW;
     const bool live = c < a.W;
     const int bs = a.W / a.blocks, blk = live ? c / bs : 0, j = live ? c % bs : 0;
     const int go = blk * 2 * bs + j; // column of this channel's r logit in a G row; the i logit sits bs further
     const float rb = live ? a.gate_bias[go] : 0.0f, ib = live ? a.gate_bias[go + bs] : 0.0f;
     const float sp8 = live ? 8.0f * softplusf_(a.lam[c]) : 0.0f, yb = live ? a.y_bias[c] : 0.0f;
-    const int groups = n >= 8 * RGLRU_GROUPS ? RGLRU_GROUPS : 1;
     const int chunk = (n + groups - 1) / groups, t0 = g * chunk, t1 = t0 + chunk < n ? t0 + chunk : n;
     auto coef = [&](int t, float &av, float &bv) {
         const float *gr = G + (size_t)t * ldg + go;
@@ -230,28 +260,62 @@ __global__ void __launch_bounds__(32 * RGLRU_GROUPS) k_rglru_scan(const float *_
         av = expf(la);
         bv = sqrtf(-expm1f(2.0f * la)) * sigmoidf_(gr[bs] + ib) * U[(size_t)t * ldu + c]; // 1 - a^2 = -expm1(2 log a)
     };
+    auto emit = [&](int t, float s) {
+        const float o = s * act_apply(ACT_GELU_TANH, PY[(size_t)t * ldp + c] + yb);
+        if (out32) out32[(size_t)t * ldo + c] = o;
+        if (out16) out16[(size_t)t * ldo + c] = __float2bfloat16_rn(o);
+    };
     float s = (st->pos == 0 || !live) ? 0.0f : S[c];
-    if (groups > 1) {
-        float A = 1.0f, B = 0.0f;
-        if (live && g < groups)
+    if (groups == 1) {
+        if (!live) return;
+        for (int t = 0; t < n; t++) {
+            float av, bv;
+            coef(t, av, bv);
+            s = fmaf(av, s, bv);
+            emit(t, s);
+        }
+        S[c] = s;
+        return;
+    }
+    const bool keep = chunk <= RGLRU_KEEP;
+    float ka[RGLRU_KEEP], kb[RGLRU_KEEP];
+    float A = 1.0f, B = 0.0f;
+    if (live) {
+        if (keep) {
+#pragma unroll
+            for (int i = 0; i < RGLRU_KEEP; i++)
+                if (t0 + i < t1) {
+                    coef(t0 + i, ka[i], kb[i]);
+                    A *= ka[i];
+                    B = fmaf(ka[i], B, kb[i]);
+                }
+        } else {
             for (int t = t0; t < t1; t++) {
                 float av, bv;
                 coef(t, av, bv);
                 A *= av;
                 B = fmaf(av, B, bv);
             }
-        cA[g][cl] = A; cB[g][cl] = B;
-        __syncthreads();
-        for (int k = 0; k < g; k++) s = fmaf(cA[k][cl], s, cB[k][cl]);
+        }
     }
-    if (!live || g >= groups) return;
-    for (int t = t0; t < t1; t++) {
-        float av, bv;
-        coef(t, av, bv);
-        s = fmaf(av, s, bv);
-        const float o = s * act_apply(ACT_GELU_TANH, PY[(size_t)t * ldp + c] + yb);
-        if (out32) out32[(size_t)t * ldo + c] = o;
-        if (out16) out16[(size_t)t * ldo + c] = __float2bfloat16_rn(o);
+    cA[g][cl] = A; cB[g][cl] = B;
+    __syncthreads();
+    if (!live) return;
+    for (int k = 0; k < g; k++) s = fmaf(cA[k][cl], s, cB[k][cl]);
+    if (keep) {
+#pragma unroll
+        for (int i = 0; i < RGLRU_KEEP; i++)
+            if (t0 + i < t1) {
+                s = fmaf(ka[i], s, kb[i]);
+                emit(t0 + i, s);
+            }
+    } else {
+        for (int t = t0; t < t1; t++) {
+            float av, bv;
+            coef(t, av, bv);
+            s = fmaf(av, s, bv);
+            emit(t, s);
+        }
     }
     if (t1 == n && t0 < n) S[c] = s;
 }
@@ -260,9 +324,9 @@ __global__ void __launch_bounds__(32 * RGLRU_GROUPS) k_rglru_scan(const float *_
 // State-space recurrence with a matrix state per head.  XBC [n][ldx] = [x: heads * P | B: groups * N | C: groups * N] (convolved,
 // SiLU applied), DT [n][lddt]: dt before its bias and softplus.  Per head h (group h / (heads / groups)):
 //   dt = softplus(DT + dt_bias),  S <- exp(-exp(a_log) dt) S + dt B x^T  (S [N][P], zero at position 0),  y = S^T C + D x.
-// grid (heads, ceil(P / SSD_COLS)), SSD_THREADS threads: sixteen lanes share a state column, lane `slice` holds rows slice + 16 i,
-// i < R, in registers (R = ceil(N / 16) rounded up to a power of two; rows beyond N stay zero); tokens are staged SSD_TB at a time
-// in shared memory.  The state is kept in the kernel's own order: ssd_state_floats() floats per layer run.
+// grid (heads, ceil(P / SSD_COLS)), SSD_THREADS threads: sixteen lanes share a state column, lane `slice` holds R of its rows (see ssd_rows)
+// in registers (R = ceil(N / 16) rounded up to a power of two; rows beyond N stay zero); tokens are staged 8 or 16 at a time
+// in shared memory (double buffered).  The state is kept in the kernel's own order: ssd_state_floats() floats per layer run.
 // ---------------------------------------------------------------------------------------------------------------------
 struct SsdArgs {
     int heads, groups, N, P;
@@ -270,14 +334,37 @@ struct SsdArgs {
 };
 #define SSD_COLS 16
 #define SSD_THREADS (SSD_COLS * 16)
-#define SSD_TB 8
+#define SSD_TB_OF(R) ((R) >= 16 ? 8 : 16) // tokens per staged batch: two buffers of B and C rows stay below 48 KB of static shared memory
 __host__ __device__ inline int ssd_reg_rows(int N) { const int q = (N + 15) / 16; return q <= 1 ? 1 : q <= 2 ? 2 : q <= 4 ? 4 : q <= 8 ? 8 : q <= 16 ? 16 : 0; }
 __host__ __device__ inline size_t ssd_state_floats(int heads, int N, int P) { return (size_t)heads * ((P + SSD_COLS - 1) / SSD_COLS) * ssd_reg_rows(N) * SSD_THREADS; }
 
+// The R state rows of lane `slice` out of a staged token's 16 R rows: for R a multiple of 4 the rows (16 k + slice) * 4 + j, j < 4,
+// k < R / 4 (sixteen lanes read consecutive 16-byte words: no bank conflicts), else the rows slice * R + i.
+template <int R>
+__device__ __forceinline__ void ssd_rows(const float *tile, int slice, float (&v)[R]) {
+    if constexpr (R % 4 == 0) {
+#pragma unroll
+        for (int k = 0; k < R / 4; k++) {
+            const float4 q = *reinterpret_cast<const float4 *>(tile + (16 * k + slice) * 4);
+            v[4 * k] = q.x; v[4 * k + 1] = q.y; v[4 * k + 2] = q.z; v[4 * k + 3] = q.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < R; i++) v[i] = tile[slice * R + i];
+    }
+}
+
+// Tokens are staged SSD_TB_OF(R) at a time through two shared-memory buffers with cp.async: the next batch's B, C, x and dt land
+// while this one is computed.  Lane t of every sixteen turns token t's dt into (step, decay) once per batch; the column's lanes
+// fetch them with a shuffle.
 template <int R>
 __global__ void __launch_bounds__(SSD_THREADS) k_ssd_scan(const float *__restrict__ XBC, int ldx, const float *__restrict__ DT, int lddt, SsdArgs a, float *__restrict__ S, int n,
                                                           const StepState *__restrict__ st, float *__restrict__ Y, int ldy) {
-    __shared__ float Bs[SSD_TB][R * 16], Cs[SSD_TB][R * 16], xs[SSD_TB][SSD_COLS], dec[SSD_TB], dts[SSD_TB];
+    constexpr int RW = R * 16;                  // staged state rows per token (rows beyond N are zero)
+    constexpr int SSD_TB = SSD_TB_OF(R);
+    constexpr int LB = SSD_TB * R / 16;         // elements of a batch's B (or C) tile per thread
+    __shared__ __align__(16) float Bs[2][SSD_TB][RW], Cs[2][SSD_TB][RW];
+    __shared__ float xs[2][SSD_TB][SSD_COLS], draw[2][16];
     const int h = blockIdx.x, tid = threadIdx.x, slice = tid & 15, cc = tid >> 4, col = blockIdx.y * SSD_COLS + cc;
     const int grp = h / (a.heads / a.groups);
     const int xo = h * a.P, bo = a.heads * a.P + grp * a.N, co = a.heads * a.P + a.groups * a.N + grp * a.N;
@@ -287,32 +374,72 @@ __global__ void __launch_bounds__(SSD_THREADS) k_ssd_scan(const float *__restric
 #pragma unroll
     for (int i = 0; i < R; i++) s[i] = fresh ? 0.0f : Sg[(size_t)i * SSD_THREADS];
     const float na = -expf(a.a_log[h]), dtb = a.dt_bias[h], Dh = a.D[h];
-    for (int t0 = 0; t0 < n; t0 += SSD_TB) {
+    const int xt = tid / SSD_COLS, xi = tid % SSD_COLS, xg = blockIdx.y * SSD_COLS + xi;
+    // element e = tid + k * SSD_THREADS of a batch's [SSD_TB][RW] tile: token e / RW, state row e % RW
+    auto fetch = [&](int t0, int buf) {
         const int nt = n - t0 < SSD_TB ? n - t0 : SSD_TB;
-        __syncthreads(); // the previous batch is consumed
-        for (int e = tid; e < nt * R * 16; e += SSD_THREADS) {
-            const int t = e / (R * 16), i = e % (R * 16);
-            const float *row = XBC + (size_t)(t0 + t) * ldx;
-            Bs[t][i] = i < a.N ? row[bo + i] : 0.0f;
-            Cs[t][i] = i < a.N ? row[co + i] : 0.0f;
+#pragma unroll
+        for (int k = 0; k < LB; k++) {
+            const int e = tid + k * SSD_THREADS, t = e / RW, i = e % RW;
+            const bool ok = t < nt && i < a.N;
+            const float *row = XBC + (size_t)(t0 + (ok ? t : 0)) * ldx;
+            cp_async4(&Bs[buf][0][0] + e, ok ? row + bo + i : XBC, ok);
+            cp_async4(&Cs[buf][0][0] + e, ok ? row + co + i : XBC, ok);
         }
-        for (int e = tid; e < nt * SSD_COLS; e += SSD_THREADS) {
-            const int t = e / SSD_COLS, i = e % SSD_COLS, cg = blockIdx.y * SSD_COLS + i;
-            xs[t][i] = cg < a.P ? XBC[(size_t)(t0 + t) * ldx + xo + cg] : 0.0f;
+        if (xt < SSD_TB) {
+            const bool ok = xt < nt && xg < a.P;
+            cp_async4(&xs[buf][xt][xi], ok ? XBC + (size_t)(t0 + xt) * ldx + xo + xg : XBC, ok);
         }
-        if (tid < nt) {
-            const float dt = softplusf_(DT[(size_t)(t0 + tid) * lddt + h] + dtb);
-            dts[tid] = dt;
-            dec[tid] = expf(na * dt);
+        if (tid < 16) cp_async4(&draw[buf][tid], tid < nt ? DT + (size_t)(t0 + tid) * lddt + h : DT, tid < nt);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(0, 0);
+    int buf = 0;
+    for (int t0 = 0; t0 < n; t0 += SSD_TB, buf ^= 1) {
+        const int nt = n - t0 < SSD_TB ? n - t0 : SSD_TB;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads(); // this batch has landed for every thread, and the other buffer's batch is consumed
+        if (t0 + SSD_TB < n) fetch(t0 + SSD_TB, buf ^ 1);
+        const float my_dt = softplusf_(draw[buf][slice] + dtb), my_dec = expf(na * my_dt); // token `slice` of the batch
+        int tb = 0;
+        for (; tb + 4 <= nt; tb += 4) { // four tokens: four independent read-out sums, reduced over the sixteen lanes with five shuffles
+            float acc[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int t = tb + u;
+                const float dA = __shfl_sync(0xffffffffu, my_dec, t, 16), dx = __shfl_sync(0xffffffffu, my_dt, t, 16) * xs[buf][t][cc];
+                float bv[R], cv[R];
+                ssd_rows<R>(Bs[buf][t], slice, bv);
+                ssd_rows<R>(Cs[buf][t], slice, cv);
+                float ac = 0.0f;
+#pragma unroll
+                for (int i = 0; i < R; i++) {
+                    s[i] = fmaf(dA, s[i], dx * bv[i]);
+                    ac = fmaf(s[i], cv[i], ac);
+                }
+                acc[u] = ac;
+            }
+            const bool hi8 = slice & 8, hi4 = slice & 4;
+            float p0 = hi8 ? acc[2] : acc[0], p1 = hi8 ? acc[3] : acc[1];
+            p0 += __shfl_xor_sync(0xffffffffu, hi8 ? acc[0] : acc[2], 8);
+            p1 += __shfl_xor_sync(0xffffffffu, hi8 ? acc[1] : acc[3], 8);
+            float v = hi4 ? p1 : p0;
+            v += __shfl_xor_sync(0xffffffffu, hi4 ? p0 : p1, 4);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            const int t = tb + (slice >> 2); // lanes 0, 4, 8, 12 of a column hold the sums of tokens tb .. tb + 3
+            if ((slice & 3) == 0 && col < a.P) Y[(size_t)(t0 + t) * ldy + xo + col] = fmaf(Dh, xs[buf][t][cc], v);
         }
-        __syncthreads();
-        for (int t = 0; t < nt; t++) {
-            const float dA = dec[t], xv = xs[t][cc], dx = dts[t] * xv;
+        for (int t = tb; t < nt; t++) {
+            const float dA = __shfl_sync(0xffffffffu, my_dec, t, 16), xv = xs[buf][t][cc], dx = __shfl_sync(0xffffffffu, my_dt, t, 16) * xv;
+            float bv[R], cv[R];
+            ssd_rows<R>(Bs[buf][t], slice, bv);
+            ssd_rows<R>(Cs[buf][t], slice, cv);
             float acc = 0.0f;
 #pragma unroll
             for (int i = 0; i < R; i++) {
-                s[i] = fmaf(dA, s[i], dx * Bs[t][slice + 16 * i]);
-                acc = fmaf(s[i], Cs[t][slice + 16 * i], acc);
+                s[i] = fmaf(dA, s[i], dx * bv[i]);
+                acc = fmaf(s[i], cv[i], acc);
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 8);
             acc += __shfl_xor_sync(0xffffffffu, acc, 4);
@@ -325,22 +452,22 @@ __global__ void __launch_bounds__(SSD_THREADS) k_ssd_scan(const float *__restric
     for (int i = 0; i < R; i++) Sg[(size_t)i * SSD_THREADS] = s[i];
 }
 
-// out = GN(y * silu(z); w) with GN an RMS norm in `groups` equal consecutive parts of the row (n_in entries).  One CTA per row,
-// dynamic shared memory: n_in floats.
-__global__ void __launch_bounds__(256) k_gated_group_norm(const float *__restrict__ Yv, int ldy, const float *__restrict__ Z, int ldz, const float *__restrict__ w, int n_in,
+// out = GN(y * silu(z); w) with GN an RMS norm in `groups` equal consecutive parts of the row (n_in entries).  One CTA per row (any
+// multiple of 32 threads), dynamic shared memory: n_in floats.
+__global__ void __launch_bounds__(1024) k_gated_group_norm(const float *__restrict__ Yv, int ldy, const float *__restrict__ Z, int ldz, const float *__restrict__ w, int n_in,
                                                           int groups, float eps, float *__restrict__ out32, bf16 *__restrict__ out16, int ldo) {
     extern __shared__ __align__(16) float gv[];
     __shared__ float red[32];
     __shared__ float inv[LY_OUTNORM_MAX_GROUPS];
     const int r = blockIdx.x;
-    for (int i = threadIdx.x; i < n_in; i += 256) {
+    for (int i = threadIdx.x; i < n_in; i += blockDim.x) {
         const float z = Z[(size_t)r * ldz + i];
         gv[i] = Yv[(size_t)r * ldy + i] * (z / (1.0f + expf(-z)));
     }
     __syncthreads();
     group_inv_rms(gv, n_in, groups, eps, inv, red);
     const int part = n_in / groups;
-    for (int i = threadIdx.x; i < n_in; i += 256) {
+    for (int i = threadIdx.x; i < n_in; i += blockDim.x) {
         const float v = gv[i] * inv[i / part] * w[i];
         if (out32) out32[(size_t)r * ldo + i] = v;
         if (out16) out16[(size_t)r * ldo + i] = __float2bfloat16_rn(v);

@@ -153,7 +153,7 @@ int b200_plan_create(const b200_config *cfg, const b200_tensor *tensors, int32_t
 #define B200_MOE_SIGMOID_INPUT 0 /* s = sigmoid(z); the `top` largest; the score scales what the expert READS; no renormalisation */
 #define B200_MOE_SOFTMAX_OUTPUT 1 /* s = softmax(z) over experts + identity experts; the `top` largest of s + "<layer>.mlp.correction" are chosen;
                                    * weights s / (sum of the chosen s + 1e-20) * moe_scale multiply the experts' OUTPUTS; the last moe_identity router
-                                   * outputs are identity experts (output = input, no tensors) */
+                                   * outputs belong to identity experts, which return what they read and own no tensors */
 #define B200_ROPE_HALF 0        /* pair (i, i + rot_dims / 2) */
 #define B200_ROPE_INTERLEAVED 1 /* pair (2i, 2i + 1) */
 #define B200_BLOCK_SANDWICH 0 /* x += N(mixer(N x)); x += N(ff(N x)) with (1 + w)-weighted RMS norms (Pibidra) */

@@ -286,6 +286,18 @@ def test_each_block_mechanism_alone(pkg):
             assert rel_rms(ref_tr[2], w64(w)["embed"][np.asarray(toks)]) < 1e-12
 
 
+def test_wide_rows(pkg):
+    """A residual row and a state-space read-out of 2048 entries: the single-row launches of the decode step run with more threads
+    per row than the chunk's."""
+    S = pkg.synth
+    mlp = S.dinuzen_moe(2, 1, 16, identity=1, scale=1.5, shared=16)
+    cfg = S.dinuzen_config(2048, 64, [S.dinuzen_mamba2(4, 512, 4, 1, 2, mlp, norm_groups=4), S.dinuzen_rglru(32, 2, 2, None)], groups=8)
+    toks = np.random.default_rng(3).integers(0, 64, 12).tolist()
+    w = S.dinuzen_weights(cfg, 31)
+    assert min_margin(oracle(), cfg, w64(w), toks) > 2e-5
+    _check_f32(pkg, cfg, w, toks, "wide", sizes=(3, 1, 2))
+
+
 def test_each_attention_mechanism_alone(pkg):
     """The same for the differential attention: a lambda far from its start value (large lq / lk), diff near one and zero, a cap
     that binds (scores far above it) and no cap, q / k norm weights of both signs, rotation over the whole slice with a small base,
