@@ -1043,7 +1043,7 @@ static int ly_time_kernel(b200_plan *p, int which, int reps, float *avg_ms, int6
     CK(cudaSetDevice(p->device));
     CK(cudaStreamSynchronize(p->stream));
     int launches = 0, rc;
-    int64_t bytes = 0;
+    int64_t bytes = 0, sum_bytes = 0; // layers may differ: the answer is the mean over the timed launches
     auto one = [&](const LyLayer *L) -> int {
         switch (which) {
         case 0: if (!L->w_gu) return B200_OK; bytes = (int64_t)2 * L->s.ff_dim * E * 2; launches++;
@@ -1067,7 +1067,12 @@ static int ly_time_kernel(b200_plan *p, int which, int reps, float *avg_ms, int6
     launches = 0;
     CK(cudaEventRecord(p->ev0, p->stream));
     for (int r = 0; r < reps; r++)
-        for (const LyLayer &L : Y.layers) { if ((rc = one(&L))) return rc; if (which == 4) break; }
+        for (const LyLayer &L : Y.layers) {
+            const int before = launches;
+            if ((rc = one(&L))) return rc;
+            if (launches > before) sum_bytes += bytes;
+            if (which == 4) break;
+        }
     CK(cudaEventRecord(p->ev1, p->stream));
     CK(cudaStreamSynchronize(p->stream));
     float ms = 0.f;

@@ -109,13 +109,17 @@ __global__ void __launch_bounds__(NTH) k_outnorm_rows(OutNormArgs a) {
         __syncthreads();
         if (a.ys) {
             const float sgv = a.shared ? sigmoidf_(a.sg[(size_t)r * a.sg_ld]) : 0.0f;
-            if (slots) { // one chosen expert per pass over the row (every thread its own entries): the loads of a pass are independent
-                for (int i = tid; i < E; i += nth) yv[i] = a.shared ? sgv * a.shared[src + i] : 0.0f;
-                for (int k = 0; k < a.top; k++) {
-                    const float wk = s_wt[k];
-                    const float *v = s_row[k] >= 0 ? a.ys + s_row[k] : row;
-#pragma unroll 4
-                    for (int i = tid; i < E; i += nth) yv[i] = fmaf(wk, v[i], yv[i]);
+            if (slots) { // per entry, the chosen experts' loads are issued eight at a time before the first of them is used
+                for (int i = tid; i < E; i += nth) {
+                    float s = a.shared ? sgv * a.shared[src + i] : 0.0f;
+                    for (int k0 = 0; k0 < a.top; k0 += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int u = 0; u < 8; u++) v[u] = k0 + u < a.top ? (s_row[k0 + u] >= 0 ? __ldg(a.ys + s_row[k0 + u] + i) : row[i]) : 0.0f;
+#pragma unroll
+                        for (int u = 0; u < 8; u++) if (k0 + u < a.top) s = fmaf(s_wt[k0 + u], v[u], s);
+                    }
+                    yv[i] = s;
                 }
             } else {
                 for (int i = tid; i < E; i += nth) {
@@ -140,14 +144,19 @@ __global__ void __launch_bounds__(NTH) k_outnorm_rows(OutNormArgs a) {
         const float *dw = depth ? s_dwa : a.dwa;
         float *mine = a.stash + (size_t)a.stash_idx * a.stash_stride + src;
         for (int i = tid; i < E; i += nth) mine[i] = row[i];
-        if (dw) {
+        if (dw) { // per entry, the earlier results' loads are issued eight at a time before the first of them is used
             const float wl = dw[a.stash_idx];
-            for (int i = tid; i < E; i += nth) row[i] *= wl;
-            for (int j = 0; j < a.stash_idx; j++) { // one earlier result per pass: its loads are independent of one another
-                const float wj = dw[j];
-                const float *sj = a.stash + (size_t)j * a.stash_stride + src;
-#pragma unroll 4
-                for (int i = tid; i < E; i += nth) row[i] = fmaf(wj, __ldg(sj + i), row[i]);
+            const float *s0 = a.stash + src;
+            for (int i = tid; i < E; i += nth) {
+                float acc = row[i] * wl;
+                for (int j0 = 0; j0 < a.stash_idx; j0 += 8) {
+                    float v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; u++) v[u] = j0 + u < a.stash_idx ? __ldg(s0 + (size_t)(j0 + u) * a.stash_stride + i) : 0.0f;
+#pragma unroll
+                    for (int u = 0; u < 8; u++) if (j0 + u < a.stash_idx) acc = fmaf(dw[j0 + u], v[u], acc);
+                }
+                row[i] = acc;
             }
         }
     }
@@ -218,7 +227,7 @@ __global__ void __launch_bounds__(256) k_conv_rows(const float *__restrict__ P, 
         const float x = back <= r ? P[(size_t)(r - back) * ldp + c_off + c] + bi : cstate[(size_t)((pos - back) % a.cring) * a.C + c];
         acc = fmaf(a.w[(size_t)c * a.taps + m], x, acc);
     }
-    cstate[(size_t)(pos % a.cring) * a.C + c] = P[(size_t)r * ldp + c_off + c] + bi;
+    if (r + a.taps > (int)gridDim.x) cstate[(size_t)(pos % a.cring) * a.C + c] = P[(size_t)r * ldp + c_off + c] + bi; // a later launch reads at most taps - 1 rows back
     if (a.silu) acc = acc / (1.0f + expf(-acc));
     if (out32) out32[(size_t)r * ldo + c] = acc;
     if (out16) out16[(size_t)r * ldo16 + c] = __float2bfloat16_rn(acc);

@@ -40,7 +40,7 @@ def configs(S):
         # shapes the tensor-core prefill takes: widths in whole GEMM tiles, (key, value) sizes 64 / 64 and 128 / 128, expert widths of 64
         "tiles_a": S.dinuzen_config(128, 256, [A(2, 1, 64, 64, D(256)), R(128, 2, 4, X(4, 2, 64, identity=1, scale=2.0, shared=128)), M(2, 64, 32, 1, 4, X(3, 2, 128, shared=None)),
                                                A(4, 1, 64, 64, X(4, 3, 64, identity=2, shared=128), kv_from=0)], groups=4),
-        "tiles_b": S.dinuzen_config(256, 384, [M(4, 32, 64, 2, 3, D(128), norm_groups=2), A(2, 2, 128, 128, X(6, 2, 64, identity=0, scale=2.5, shared=256), rot_dims=32),
+        "tiles_b": S.dinuzen_config(256, 384, [M(4, 32, 64, 2, 3, D(128), norm_groups=2), A(2, 2, 128, 128, X(6, 2, 64, identity=0, scale=1.75, shared=256), rot_dims=32),
                                                R(256, 4, 2, None), A(2, 2, 128, 128, D(384), rot_dims=32, kv_from=1)], groups=2),
     }
 

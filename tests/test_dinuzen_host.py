@@ -184,22 +184,22 @@ def test_router_and_experts():
     E, X, I = 10, 4, 2
     w = {"router": rng.standard_normal((X + I, E)), "correction": np.zeros(X + I)}
     x = rng.standard_normal((8, E))
-    r = {"experts": X, "identity": I, "top": 3, "scale": 2.5}
+    r = {"experts": X, "identity": I, "top": 3, "scale": 1.75}
     ids, wts = O.moe_route(x, w, "", r)
     z = x @ w["router"].T
-    assert np.array_equal(ids, np.argsort(-z, axis=-1, kind="stable")[:, :3]) and np.allclose(wts.sum(-1), 2.5)   # renormalised over the chosen, times scale
+    assert np.array_equal(ids, np.argsort(-z, axis=-1, kind="stable")[:, :3]) and np.allclose(wts.sum(-1), 1.75)   # renormalised over the chosen, times scale
     # the correction moves the CHOICE, the weights still come from the plain scores
     w2 = dict(w, correction=np.array([0, 0, 0, 0, 0, 5.0]))
     ids2, wts2 = O.moe_route(x, w2, "", r)
     assert np.all(ids2[:, 0] == 5)
     s = np.exp(z - z.max(-1, keepdims=True)); s /= s.sum(-1, keepdims=True)
-    assert np.allclose(wts2, np.take_along_axis(s, ids2, -1) / np.take_along_axis(s, ids2, -1).sum(-1, keepdims=True) * 2.5)
+    assert np.allclose(wts2, np.take_along_axis(s, ids2, -1) / np.take_along_axis(s, ids2, -1).sum(-1, keepdims=True) * 1.75)
     # identity experts return their input; with only identity experts chosen the mixture is scale * x
     for e in range(X):
         w[f"e{e}.gate"], w[f"e{e}.up"], w[f"e{e}.down"] = rng.standard_normal((6, E)), rng.standard_normal((6, E)), rng.standard_normal((E, 6))
     w3 = dict(w, correction=np.array([0, 0, 0, 0, 9.0, 9.0]))
     out = O.ff_moe(x, w3, "", {"router": dict(r, top=2), "expert": {"ff": 6}, "shared": None})
-    assert np.allclose(out, 2.5 * x)
+    assert np.allclose(out, 1.75 * x)
     # a shared expert is added for every token, times ONE sigmoid gate per token
     w3.update({"shared.gate": rng.standard_normal((5, E)), "shared.up": rng.standard_normal((5, E)), "shared.down": rng.standard_normal((E, 5)), "shared.sg": rng.standard_normal((1, E))})
     out2 = O.ff_moe(x, w3, "", {"router": dict(r, top=2), "expert": {"ff": 6}, "shared": {"ff": 5}})
