@@ -374,9 +374,9 @@ static int ly_enqueue_outnorm(b200_plan *p, bool decode, int n, const StepState 
             ly::RglruArgs ra{};
             ra.W = W; ra.blocks = nb; ra.gate_bias = L.gate_bias; ra.lam = L.lam; ra.y_bias = L.y_bias;
             // a chunk: 16 channels x up to 32 row groups per CTA (the last group may be short, never empty rows in between); few rows: 32 channels, one group
-            if (n >= 64) rc = launch_k(p, false, ly::k_rglru_scan<16>, dim3((W + 15) / 16), dim3(16 * RGLRU_MAX_GROUPS), (size_t)0, (const float *)Y.DLT, Y.maxD, (const float *)Y.Q, Y.maxQ,
+            if (n >= 64) rc = launch_k(p, false, ly::k_rglru_scan<16, RGLRU_MAX_GROUPS>, dim3((W + 15) / 16), dim3(16 * RGLRU_MAX_GROUPS), (size_t)0, (const float *)Y.DLT, Y.maxD, (const float *)Y.Q, Y.maxQ,
                                        (const float *)(Y.PROJ + W), Y.maxP, ra, R.S, n, st, att32, att16, L.gd);
-            else rc = launch_k(p, false, ly::k_rglru_scan<32>, dim3((W + 31) / 32), dim3(32), (size_t)0, (const float *)Y.DLT, Y.maxD, (const float *)Y.Q, Y.maxQ,
+            else rc = launch_k(p, false, ly::k_rglru_scan<32, 1>, dim3((W + 31) / 32), dim3(32), (size_t)0, (const float *)Y.DLT, Y.maxD, (const float *)Y.Q, Y.maxQ,
                                (const float *)(Y.PROJ + W), Y.maxP, ra, R.S, n, st, att32, att16, L.gd);
             if (rc) return rc;
             nl += 3;

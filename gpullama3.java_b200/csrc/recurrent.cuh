@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(NTH) k_outnorm_rows(OutNormArgs a) {
         __syncthreads();
         if (a.ys) {
             const float sgv = a.shared ? sigmoidf_(a.sg[(size_t)r * a.sg_ld]) : 0.0f;
-            if (slots) { // per entry, the chosen experts' loads are issued eight at a time before the first of them is used
+            if (slots && NTH >= 1024) { // a single wide row: per entry, the chosen experts' loads are issued eight at a time before the first is used
                 for (int i = tid; i < E; i += nth) {
                     float s = a.shared ? sgv * a.shared[src + i] : 0.0f;
                     for (int k0 = 0; k0 < a.top; k0 += 8) {
@@ -120,6 +120,14 @@ __global__ void __launch_bounds__(NTH) k_outnorm_rows(OutNormArgs a) {
                         for (int u = 0; u < 8; u++) if (k0 + u < a.top) s = fmaf(s_wt[k0 + u], v[u], s);
                     }
                     yv[i] = s;
+                }
+            } else if (slots) { // many rows: one chosen expert per pass over the row, the loads of a pass are independent and the CTAs many
+                for (int i = tid; i < E; i += nth) yv[i] = a.shared ? sgv * a.shared[src + i] : 0.0f;
+                for (int k = 0; k < a.top; k++) {
+                    const float wk = s_wt[k];
+                    const float *v = s_row[k] >= 0 ? a.ys + s_row[k] : row;
+#pragma unroll 4
+                    for (int i = tid; i < E; i += nth) yv[i] = fmaf(wk, v[i], yv[i]);
                 }
             } else {
                 for (int i = tid; i < E; i += nth) {
@@ -144,7 +152,7 @@ __global__ void __launch_bounds__(NTH) k_outnorm_rows(OutNormArgs a) {
         const float *dw = depth ? s_dwa : a.dwa;
         float *mine = a.stash + (size_t)a.stash_idx * a.stash_stride + src;
         for (int i = tid; i < E; i += nth) mine[i] = row[i];
-        if (dw) { // per entry, the earlier results' loads are issued eight at a time before the first of them is used
+        if (dw && NTH >= 1024) { // a single wide row: per entry, the earlier results' loads are issued eight at a time
             const float wl = dw[a.stash_idx];
             const float *s0 = a.stash + src;
             for (int i = tid; i < E; i += nth) {
@@ -157,6 +165,15 @@ __global__ void __launch_bounds__(NTH) k_outnorm_rows(OutNormArgs a) {
                     for (int u = 0; u < 8; u++) if (j0 + u < a.stash_idx) acc = fmaf(dw[j0 + u], v[u], acc);
                 }
                 row[i] = acc;
+            }
+        } else if (dw) { // many rows: one earlier result per pass
+            const float wl = dw[a.stash_idx];
+            for (int i = tid; i < E; i += nth) row[i] *= wl;
+            for (int j = 0; j < a.stash_idx; j++) {
+                const float wj = dw[j];
+                const float *sj = a.stash + (size_t)j * a.stash_stride + src;
+#pragma unroll 4
+                for (int i = tid; i < E; i += nth) row[i] = fmaf(wj, __ldg(sj + i), row[i]);
             }
         }
     }
@@ -251,11 +268,11 @@ struct RglruArgs {
 };
 #define RGLRU_MAX_GROUPS 32
 #define RGLRU_KEEP 16
-template <int CW>
-__global__ void __launch_bounds__(CW * RGLRU_MAX_GROUPS) k_rglru_scan(const float *__restrict__ U, int ldu, const float *__restrict__ G, int ldg, const float *__restrict__ PY, int ldp,
+template <int CW, int MAXG> // MAXG = 1: the one-group form only (a launch of CW threads)
+__global__ void __launch_bounds__(CW * MAXG) k_rglru_scan(const float *__restrict__ U, int ldu, const float *__restrict__ G, int ldg, const float *__restrict__ PY, int ldp,
                                                                       RglruArgs a, float *__restrict__ S, int n, const StepState *__restrict__ st, float *__restrict__ out32,
                                                                       bf16 *__restrict__ out16, int ldo) {
-    __shared__ float cA[RGLRU_MAX_GROUPS][CW], cB[RGLRU_MAX_GROUPS][CW];
+    __shared__ float cA[MAXG][CW], cB[MAXG][CW];
     const int cl = threadIdx.x % CW, g = threadIdx.x / CW, c = blockIdx.x * CW + cl, groups = blockDim.x / CW;
     const bool live = c < a.W;
     const int bs = a.W / a.blocks, blk = live ? c / bs : 0, j = live ? c % bs : 0;
@@ -286,15 +303,28 @@ __global__ void __launch_bounds__(CW * RGLRU_MAX_GROUPS) k_rglru_scan(const floa
         S[c] = s;
         return;
     }
+    if constexpr (MAXG == 1) return;
     const bool keep = chunk <= RGLRU_KEEP;
-    float ka[RGLRU_KEEP], kb[RGLRU_KEEP];
+    float ka[RGLRU_KEEP], kb[RGLRU_KEEP], ku[RGLRU_KEEP], kp[RGLRU_KEEP];
     float A = 1.0f, B = 0.0f;
     if (live) {
-        if (keep) {
+        if (keep) { // all of the group's loads (both gate logits, the input, the other branch) are in flight before the first is used
+#pragma unroll
+            for (int i = 0; i < RGLRU_KEEP; i++) {
+                const bool in = t0 + i < t1;
+                const size_t t = in ? t0 + i : 0;
+                ka[i] = in ? __ldg(G + t * ldg + go) : 0.0f;
+                kb[i] = in ? __ldg(G + t * ldg + go + bs) : 0.0f;
+                ku[i] = in ? __ldg(U + t * ldu + c) : 0.0f;
+                kp[i] = in ? __ldg(PY + t * ldp + c) : 0.0f;
+            }
 #pragma unroll
             for (int i = 0; i < RGLRU_KEEP; i++)
                 if (t0 + i < t1) {
-                    coef(t0 + i, ka[i], kb[i]);
+                    const float la = -sp8 * sigmoidf_(ka[i] + rb);
+                    ka[i] = expf(la);
+                    kb[i] = sqrtf(-expm1f(2.0f * la)) * sigmoidf_(kb[i] + ib) * ku[i];
+                    kp[i] = act_apply(ACT_GELU_TANH, kp[i] + yb);
                     A *= ka[i];
                     B = fmaf(ka[i], B, kb[i]);
                 }
@@ -316,7 +346,9 @@ __global__ void __launch_bounds__(CW * RGLRU_MAX_GROUPS) k_rglru_scan(const floa
         for (int i = 0; i < RGLRU_KEEP; i++)
             if (t0 + i < t1) {
                 s = fmaf(ka[i], s, kb[i]);
-                emit(t0 + i, s);
+                const float o = s * kp[i];
+                if (out32) out32[(size_t)(t0 + i) * ldo + c] = o;
+                if (out16) out16[(size_t)(t0 + i) * ldo + c] = __float2bfloat16_rn(o);
             }
     } else {
         for (int t = t0; t < t1; t++) {
