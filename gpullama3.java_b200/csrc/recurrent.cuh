@@ -62,8 +62,30 @@ struct OutNormArgs {
 };
 
 // Per part sums of squares of v [E] (parts of E / groups entries) -> inv[g] = 1 / sqrt(mean + eps).  inv: shared memory.
+// Several parts of a multiple of 32 entries (E <= 32 * LY_GROUP_WARP_SUMS): every warp leaves the sum of each 32 consecutive entries it
+// visits, then a warp per part adds that part's sums -- two barriers whatever the number of parts, a fixed order of additions.
+// Other shapes: one block reduction per part.
+#define LY_GROUP_WARP_SUMS 512
 __device__ __forceinline__ void group_inv_rms(const float *v, int E, int groups, float eps, float *inv, float *red) {
     const int part = E / groups;
+    if (groups > 1 && part % 32 == 0 && E <= 32 * LY_GROUP_WARP_SUMS) {
+        __shared__ float wsum[LY_GROUP_WARP_SUMS];
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5, per = part / 32;
+        for (int i0 = warp * 32; i0 < E; i0 += nw * 32) {
+            const float t = v[i0 + lane];
+            const float ss = warp_sum(t * t);
+            if (lane == 0) wsum[i0 >> 5] = ss;
+        }
+        __syncthreads();
+        for (int g = warp; g < groups; g += nw) {
+            float ss = 0.0f;
+            for (int k = lane; k < per; k += 32) ss += wsum[g * per + k];
+            ss = warp_sum(ss);
+            if (lane == 0) inv[g] = 1.0f / sqrtf(ss / (float)part + eps);
+        }
+        __syncthreads();
+        return;
+    }
     for (int g = 0; g < groups; g++) {
         float ss = 0.0f;
         for (int i = threadIdx.x; i < part; i += blockDim.x) { const float t = v[g * part + i]; ss = fmaf(t, t, ss); }
@@ -77,7 +99,7 @@ __device__ __forceinline__ void group_inv_rms(const float *v, int E, int groups,
 #define LY_OUTNORM_SLOTS 64  // chosen experts / depth weights kept in shared memory (more: read where they are)
 // One CTA of NTH threads per row.  Dynamic shared memory: 2 * E floats.
 template <int NTH>
-__global__ void __launch_bounds__(NTH) k_outnorm_rows(OutNormArgs a) {
+__global__ void __launch_bounds__(NTH, 1) k_outnorm_rows(OutNormArgs a) {
     extern __shared__ __align__(16) float smo[];
     __shared__ float red[32];
     __shared__ float inv[LY_OUTNORM_MAX_GROUPS];
