@@ -362,8 +362,8 @@ static int ly_enqueue_outnorm(b200_plan *p, bool decode, int n, const StepState 
             const int W = L.qd, nb = s.heads, bs = s.value_dim;
             ly::ConvArgs ca{};
             ca.C = W; ca.taps = s.conv_taps; ca.cring = Y.cring; ca.w = L.conv_w; ca.bias_in = L.x_bias; ca.bias_out = L.conv_b; ca.silu = 0;
-            if ((rc = launch_k(p, false, ly::k_conv_rows, dim3(n, (W + 255) / 256), dim3(256), (size_t)0, (const float *)Y.PROJ, Y.maxP, 0, ca, R.cstate, Y.DLT, Y.maxD,
-                               h16 ? Y.U16 : (ly::bf16 *)nullptr, Y.maxD, st))) return rc;
+            if ((rc = launch_k(p, false, ly::k_conv_rows, dim3((n + LY_CONV_ROWS - 1) / LY_CONV_ROWS, (W + 255) / 256), dim3(256), (size_t)0, (const float *)Y.PROJ, Y.maxP, 0, ca, R.cstate, Y.DLT, Y.maxD,
+                               h16 ? Y.U16 : (ly::bf16 *)nullptr, Y.maxD, st, n))) return rc;
             { // gate logits of every block: [r | i] rows of the block's stacked matrix times the block's channels
                 ly::GemmView gv{};
                 ly::MvView mv{};
@@ -384,8 +384,8 @@ static int ly_enqueue_outnorm(b200_plan *p, bool decode, int n, const StepState 
             const int inner = L.gd, gn = s.kv_heads * s.key_dim;
             ly::ConvArgs ca{};
             ca.C = L.dC; ca.taps = s.conv_taps; ca.cring = Y.cring; ca.w = L.conv_w; ca.bias_in = nullptr; ca.bias_out = L.conv_b; ca.silu = 1;
-            if ((rc = launch_k(p, false, ly::k_conv_rows, dim3(n, (L.dC + 255) / 256), dim3(256), (size_t)0, (const float *)Y.PROJ, Y.maxP, inner, ca, R.cstate, Y.DLT, Y.maxD,
-                               (ly::bf16 *)nullptr, 0, st))) return rc;
+            if ((rc = launch_k(p, false, ly::k_conv_rows, dim3((n + LY_CONV_ROWS - 1) / LY_CONV_ROWS, (L.dC + 255) / 256), dim3(256), (size_t)0, (const float *)Y.PROJ, Y.maxP, inner, ca, R.cstate, Y.DLT, Y.maxD,
+                               (ly::bf16 *)nullptr, 0, st, n))) return rc;
             ly::SsdArgs sa{};
             sa.heads = s.heads; sa.groups = s.kv_heads; sa.N = s.key_dim; sa.P = s.value_dim; sa.a_log = L.a_log; sa.dt_bias = L.dt_bias; sa.D = L.ssd_d;
             const dim3 grid(s.heads, (s.value_dim + SSD_COLS - 1) / SSD_COLS), block(SSD_THREADS);

@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(256) k_act_rows(const float *__restrict__ in, 
 // Causal convolution per channel.  Channel c of row r (position p = st->pos + r) reads the inputs in(p - taps + 1 .. p) with
 // in(q) = P[q's row][c_off + c] + bias_in[c]: from the rows of this launch where they belong to it, else from the ring `cstate`
 // (position q in slot q % cring, written by earlier launches; cring >= taps - 1 + rows of a launch); positions before the start
-// of the sequence count as zero.  out = act(sum_m w[c][m] in(p - taps + 1 + m) + bias_out[c]).  grid (n, ceil(C / 256)).
+// of the sequence count as zero.  out = act(sum_m w[c][m] in(p - taps + 1 + m) + bias_out[c]).  grid (ceil(n / LY_CONV_ROWS), ceil(C / 256)).
 // ---------------------------------------------------------------------------------------------------------------------
 struct ConvArgs {
     int C, taps, cring;
@@ -253,23 +253,37 @@ struct ConvArgs {
     const float *bias_out; // [C] (nullable)
     int silu;              // 1: SiLU on the result
 };
+#define LY_CONV_ROWS 4 // consecutive rows of a channel per thread: their loads are independent and in flight together
 __global__ void __launch_bounds__(256) k_conv_rows(const float *__restrict__ P, int ldp, int c_off, ConvArgs a, float *__restrict__ cstate, float *__restrict__ out32, int ldo,
-                                                   bf16 *__restrict__ out16, int ldo16, const StepState *__restrict__ st) {
-    const int r = blockIdx.x, c = blockIdx.y * 256 + threadIdx.x;
+                                                   bf16 *__restrict__ out16, int ldo16, const StepState *__restrict__ st, int n) {
+    const int r0 = blockIdx.x * LY_CONV_ROWS, c = blockIdx.y * 256 + threadIdx.x;
     if (c >= a.C) return;
-    const int pos = st->pos + r;
-    const float bi = a.bias_in ? a.bias_in[c] : 0.0f;
-    float acc = a.bias_out ? a.bias_out[c] : 0.0f;
+    const float bi = a.bias_in ? a.bias_in[c] : 0.0f, bo = a.bias_out ? a.bias_out[c] : 0.0f;
+    float acc[LY_CONV_ROWS];
+#pragma unroll
+    for (int i = 0; i < LY_CONV_ROWS; i++) acc[i] = bo;
     for (int m = 0; m < a.taps; m++) {
         const int back = a.taps - 1 - m;
-        if (pos - back < 0) continue;
-        const float x = back <= r ? P[(size_t)(r - back) * ldp + c_off + c] + bi : cstate[(size_t)((pos - back) % a.cring) * a.C + c];
-        acc = fmaf(a.w[(size_t)c * a.taps + m], x, acc);
+        const float wm = a.w[(size_t)c * a.taps + m];
+#pragma unroll
+        for (int i = 0; i < LY_CONV_ROWS; i++) {
+            const int r = r0 + i, pos = st->pos + r;
+            if (r >= n || pos - back < 0) continue;
+            const float x = back <= r ? P[(size_t)(r - back) * ldp + c_off + c] + bi : cstate[(size_t)((pos - back) % a.cring) * a.C + c];
+            acc[i] = fmaf(wm, x, acc[i]);
+        }
     }
-    if (r + a.taps > (int)gridDim.x) cstate[(size_t)(pos % a.cring) * a.C + c] = P[(size_t)r * ldp + c_off + c] + bi; // a later launch reads at most taps - 1 rows back
-    if (a.silu) acc = acc / (1.0f + expf(-acc));
-    if (out32) out32[(size_t)r * ldo + c] = acc;
-    if (out16) out16[(size_t)r * ldo16 + c] = __float2bfloat16_rn(acc);
+#pragma unroll
+    for (int i = 0; i < LY_CONV_ROWS; i++) {
+        const int r = r0 + i, pos = st->pos + r;
+        if (r >= n) break;
+        // a later launch reads at most taps - 1 rows back
+        if (r + a.taps > n) cstate[(size_t)(pos % a.cring) * a.C + c] = P[(size_t)r * ldp + c_off + c] + bi;
+        float v = acc[i];
+        if (a.silu) v = v / (1.0f + expf(-v));
+        if (out32) out32[(size_t)r * ldo + c] = v;
+        if (out16) out16[(size_t)r * ldo16 + c] = __float2bfloat16_rn(v);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
