@@ -1079,6 +1079,6 @@ static int ly_time_kernel(b200_plan *p, int which, int reps, float *avg_ms, int6
     CK(cudaEventElapsedTime(&ms, p->ev0, p->ev1));
     if (launches == 0) return fail(p, B200_ERR_UNSUPPORTED, "the plan has no such projection");
     *avg_ms = ms / launches;
-    if (algorithmic_bytes) *algorithmic_bytes = bytes;
+    if (algorithmic_bytes) *algorithmic_bytes = sum_bytes / launches;
     return B200_OK;
 }
