@@ -607,7 +607,7 @@ __global__ void __launch_bounds__(256) k_slice_norm_rope(float *__restrict__ P, 
         }
 }
 
-// Differential attention: A [n][heads][2][dv] holds the two maps' outputs per head; o = a1 - lambda a2, then o / sqrt(mean(o^2) + eps)
+// Differential attention: A [n][heads][2][dv] = per head the results of map 1 and map 2; o = a1 - lambda a2, normalised to o / sqrt(mean(o^2) + eps)
 // over the head's dv values times out_scale.  One CTA per row, a warp per head.
 __global__ void __launch_bounds__(256) k_diff_combine(const float *__restrict__ A, int lda, int heads, int dv, float lambda, float out_scale, float eps, float *__restrict__ out32,
                                                       bf16 *__restrict__ out16, int ldo) {

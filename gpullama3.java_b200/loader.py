@@ -285,7 +285,7 @@ def lerosun_configuration(cfg: dict, tensor_shapes: dict, context_length: int) -
 def dinuzen_configuration(cfg: dict, tensor_shapes: dict, context_length: int) -> LayeredConfiguration:
     """config.json of a Dinuzen model -> LayeredConfiguration: blocks with the norm on the sublayer's output, token shift and depth
     average; per layer a real-gated linear recurrent unit, a state-space recurrence or a differential attention, and a plain GELU
-    feed-forward or a softmax-routed mixture of experts.  Every size and every constant that can differ between models comes from
+    feed-forward or a softmax-routed mixture of experts.  All sizes and all model-dependent constants are read from
     the file."""
     layers = []
     for i, lc in enumerate(cfg["layers"]):

@@ -160,11 +160,11 @@ int b200_plan_create(const b200_config *cfg, const b200_tensor *tensors, int32_t
 #define B200_BLOCK_PRENORM 2  /* x += s1 * mixer(R(x; g1)); x += s2 * ff(R(x; g2)): R = RMS norm times ONE number ("<layer>.norm1", a scalar tensor),
                                * s = a vector ("<layer>.ls1"); the embedding output passes R(.; "embed.norm"); a loop block repeats without a
                                * prologue (nothing is re-added between passes) */
-#define B200_BLOCK_OUTNORM 3  /* x += s1 * GN(mixer(h); w1); x += s2 * GN(ff(x); w2): the sublayers read x itself, the norm (RMS norm in norm_groups equal
+#define B200_BLOCK_OUTNORM 3  /* x += s1 * GN(mixer(h); w1); x += s2 * GN(ff(x); w2): a sublayer's input is the stream x unnormalised, the norm (RMS norm in norm_groups equal
                                * consecutive parts, weights used as stored, "<layer>.norm1" / ".norm2") sits on the sublayer's output, s = "<layer>.ls1" /
                                * ".ls2".  token_shift: h[t] = x[t] + (x[t-1] - x[t]) * "<layer>.shift" (x[-1] = 0; the previous row is part of the
                                * sequence's state in every layer); depth_average: behind layer i, x <- sum_{j <= i+1} "<layer>.dwa"[j] X_j with X_0
-                               * the embedding output and X_(i+1) layer i's result before the averaging.  The final norm is the grouped one too */
+                               * what the embedding gave and X_(i+1) what layer i left before it was averaged.  The final norm is the grouped one too */
 #define B200_BLOCK_PARALLEL 1 /* x += residual_mult * (mixer(LN1 x) + ff(LN2 x)), layer norms with weight and bias ("<layer>.norm1", ".norm1.b", ...) */
 #define B200_ACT_GELU_TANH 0
 #define B200_ACT_SILU 1
@@ -214,8 +214,8 @@ typedef struct b200_layer_spec {
     /* B200_MIXER_GATED_DELTA */
     int32_t conv_taps;      /* taps of the causal convolution (>= 1) */
     /* B200_MIXER_WINDOW_ATTENTION in a B200_BLOCK_OUTNORM plan */
-    int32_t score_maps;     /* 2: differential attention.  q has heads * 2 * key_dim rows and k kv_heads * 2 * key_dim, head by head as [map 1 | map 2];
-                               each map is a softmax attention of its own over the same values, o = a1 - lambda a2 with lambda =
+    int32_t score_maps;     /* 2: differential attention.  q has heads * 2 * key_dim rows and k kv_heads * 2 * key_dim, ordered [head][map 1 | map 2];
+                               both maps are separate softmax attentions that share the values, o = a1 - lambda a2 with lambda =
                                exp(<lq1, lk1>) - exp(<lq2, lk2>) + diff_init ("<layer>.mix.lq1" ... [key_dim]), then o / rms(o) over the head's values
                                (no weight) times (1 - diff_init).  0 / 1: one map */
     float diff_init;
@@ -227,7 +227,7 @@ typedef struct b200_layer_spec {
     int32_t moe_router;     /* B200_MOE_* */
     int32_t moe_identity;   /* identity experts behind the ff_experts real ones */
     float moe_scale;
-    int32_t moe_shared_ff;  /* > 0: a shared expert of that width ("<layer>.mlp.shared.{gate,up,down}") runs for every token and is added times
+    int32_t moe_shared_ff;  /* > 0: a shared expert of that width ("<layer>.mlp.shared.{gate,up,down}") is evaluated for all tokens and added times
                                sigmoid(<"<layer>.mlp.shared.sg", x>) */
 } b200_layer_spec;
 

@@ -97,7 +97,7 @@ def gelu_erf(z):
 
 # ---- norms, shift, depth average ---------------------------------------------------------------------------------------
 def group_rms_norm(v, w, groups: int, eps: float):
-    """v [..., n]: every one of `groups` consecutive parts by its own root mean square; the whole times w (None: no weight)."""
+    """v [..., n]: `groups` consecutive parts, each divided by the RMS of that part alone; the whole times w (None: no weight)."""
     n = v.shape[-1]
     p = v.reshape(v.shape[:-1] + (groups, n // groups))
     p = p / np.sqrt((p * p).mean(-1, keepdims=True) + eps)
